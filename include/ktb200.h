@@ -359,7 +359,8 @@ int ktb200_mla_kv_write(void* kv_cache, int page_size, const void* ckv, const vo
  *   h of row prev_idx[t] of this launch (>= 0), else state row rd_row[t] (>= 0), else zero; h_t is stored to state row
  *   wr_row[t] when >= 0 (the caller double-buffers the state rows so that no launch reads a row it writes).
  * ktb200_latent_prep: proj row = [q latent | kv latent | rotated key part | ...]; writes RMS-normed q latent to cq_out and the
- *   RMS-normed kv latent + the rotated key part (interleaved pairs over the first rot_dims, angle pos * inv_freq[i]) into the
+ *   RMS-normed kv latent + the rotated key part (over the first rot_dims; rot_layout 0: columns 2i and 2i + 1 pair up, 1: column i
+ *   pairs with column i + rot_dims / 2; angle pos * inv_freq[i]; q_rank = 0: no query latent) into the
  *   paged cache row  page_table[slot][(pos / page_size) % max_pages] * page_size + pos % page_size  ([R + rot_dim] per row; a
  *   sequence's page table row is a ring, so a windowed sequence may grow past max_pages * page_size tokens).
  * ktb200_latent_window_attn: absorbed latent attention, sliding window (<= 0: none), soft-max sink (NULL: none);
@@ -373,11 +374,11 @@ int ktb200_mla_kv_write(void* kv_cache, int page_size, const void* ckv, const vo
 int ktb200_group_rmsnorm_shift(const float* x_in, const void* delta_a, int a_type, const void* delta_b, int b_type, float mult, float* x_out,
                                const void* weight, int groups, float eps, const void* shift, const int* prev_idx, const int* rd_row,
                                const int* wr_row, float* state, void* h_out, void* hs_out, int n_tokens, int width, int dtype, void* stream);
-int ktb200_latent_prep(const void* proj, long proj_stride, int q_rank, int kv_rank, int rot_dim, int rot_dims, const double* inv_freq,
+int ktb200_latent_prep(const void* proj, long proj_stride, int q_rank, int kv_rank, int rot_dim, int rot_dims, int rot_layout, const double* inv_freq,
                        const void* q_norm_w, const void* kv_norm_w, float eps, const int* pos, const int* slot, const int* page_table,
                        int max_pages, int page_size, void* cache, void* cq_out, int n_tokens, int dtype, void* stream);
 size_t ktb200_latent_window_attn_workspace(int n_tokens, int num_heads, int kv_rank, int splits);
-int ktb200_latent_window_attn(const void* q, const void* q_abs, int num_heads, int dim, int rot_dim, int kv_rank, int rot_dims,
+int ktb200_latent_window_attn(const void* q, const void* q_abs, int num_heads, int dim, int rot_dim, int kv_rank, int rot_dims, int rot_layout,
                               const double* inv_freq, float scale, const float* sink, int window, const int* pos, const int* slot,
                               const int* page_table, int max_pages, int page_size, const void* cache, void* out, int n_tokens, int splits,
                               void* workspace, int dtype, void* stream);
@@ -388,7 +389,7 @@ size_t ktb200_latent_window_attn_tc_workspace(int n_tokens, int num_heads, int w
 int ktb200_latent_window_attn_tc(const void* q_abs, const void* q_rot, int num_heads, float scale, const float* sink, int window, const int* pos,
                                  const int* slot, const int* page_table, int max_pages, int page_size, const void* cache, long cache_rows,
                                  void* out, int n_tokens, int max_kv, void* workspace, size_t workspace_bytes, void* stream);
-int ktb200_rope_rows(const void* q, int num_heads, int dim, int rot_dim, int rot_dims, const double* inv_freq, const int* pos, void* out,
+int ktb200_rope_rows(const void* q, int num_heads, int dim, int rot_dim, int rot_dims, int rot_layout, const double* inv_freq, const int* pos, void* out,
                      int n_tokens, int dtype, void* stream);
 int ktb200_sigmoid_gate_mul(const void* heads, const void* gate, long gate_stride, void* out, int n_tokens, int num_heads, int vdim,
                             int dtype, void* stream);
@@ -407,8 +408,9 @@ int ktb200_experts_down_by_expert(const void* act, const int64_t* ids, const flo
 /* w_gate == NULL in the four calls above: experts of two matrices, act = relu(W_up x)^2.
  *
  * Layers with norms on both sides of every sublayer, sigmoid attention and gated linear attention (csrc/seq_mixers.cu):
- *   ktb200_group_rmsnorm_sandwich   x_out = x_in + gnorm(y) * w_post + row_add ; h = gnorm(x_out) * w_pre.  x_in, w_post, row_add,
- *                                   x_out (when w_pre is given) and w_pre / h_out may be NULL; y is fp32 or bf16 (y_type).
+ *   ktb200_group_rmsnorm_sandwich   x_out = x_in + gnorm(y) * (w_post + weight_offset) + row_add ; h = gnorm(x_out) * (w_pre + weight_offset).
+ *                                   x_in, w_post, row_add, x_out (when h_out is given) and w_pre / h_out may be NULL; y is fp32 or bf16
+ *                                   (y_type); h_out without w_pre: x_out rounded to the compute dtype; weight_offset 1: zero-centred weights.
  *   ktb200_qk_norm_cache_write      proj rows [q H*d | k G*d | v G*dv | ...]: per-head RMS norm of q and k, q times
  *                                   1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1), [k | v] into the paged cache, q into q_out
  *   ktb200_sigmoid_bias_attn        out[t][h] = sigmoid(gate[t][h]) * sum_{j <= pos} sigmoid(scale q.k_j + bias[h][min(pos - j, n_bias - 1)]
@@ -420,7 +422,8 @@ int ktb200_experts_down_by_expert(const void* act, const int64_t* ids, const flo
  *   ktb200_gla_out                  out = o / sqrt(mean_vdim(o^2) + eps) * norm_w * silu(gate)
  *   ktb200_xielu                    z > 0: softplus(pq[0]) z^2 + z/2 ; else (1/2 + softplus(pq[1])) (exp(z) - 1 - z) + z/2 */
 int ktb200_group_rmsnorm_sandwich(const float* x_in, const void* y, int y_type, const void* w_post, const float* row_add, float* x_out,
-                                  const void* w_pre, void* h_out, int groups, float eps, int n_tokens, int width, int dtype, void* stream);
+                                  const void* w_pre, void* h_out, int groups, float eps, float weight_offset, int n_tokens, int width, int dtype,
+                                  void* stream);
 int ktb200_qk_norm_cache_write(const void* proj, long proj_stride, int heads, int kv_heads, int dim, int vdim, const void* q_norm_w,
                                const void* k_norm_w, float eps, float temp_coef, int temp_every, const int* pos, const int* slot,
                                const int* page_table, int max_pages, int page_size, void* cache, void* q_out, int n_tokens, int dtype,
@@ -440,6 +443,36 @@ int ktb200_gla_scan(const void* proj, long proj_stride, int q_off, int k_off, in
 int ktb200_gla_out(const float* o, const void* norm_w, float eps, const void* gate, long gate_stride, void* out, int n_tokens, int heads,
                    int vdim, int dtype, void* stream);
 int ktb200_xielu(const void* z, void* out, const float* pq, long n, int dtype, void* stream);
+/* out[t][i] = act(gate_up[t][i]) * gate_up[t][ff + i]; act 0: SiLU, 1: GELU in its tanh form */
+int ktb200_gated_act_mul(const void* gate_up, void* out, int n_tokens, int ff, int act, int dtype, void* stream);
+
+/* Soft-max attention over grouped key/value heads (csrc/softmax_attn.cu) and the gated delta rule (csrc/delta_rule.cu):
+ *   ktb200_rope_norm_cache_write   proj rows hold q [H*d] at q_off, k [G*d] at k_off, v [G*dv] at v_off: q and k turn over their first rot_dims
+ *                                  columns (rot_layout as above), are divided by sqrt(mean(x^2) + eps) per head when unit_rms, v becomes
+ *                                  (1 - blend[0]) v + blend[0] v_other[token] when v_other is given; [k | v] into the paged cache, q into q_out
+ *   ktb200_window_softmax_attn     out[t][h] = sum_j softmax_j(cap(scale q.k_j)) v_j over pos - window < j <= pos (window <= 0: all j <= pos),
+ *                                  cap(s) = c tanh(s / c), c = softcap (softcap <= 0: none); splits > 1 cuts the key range
+ *                                  (workspace: ktb200_window_softmax_attn_workspace bytes)
+ *   ktb200_delta_prep              channels [q G*d | k G*d | v H*dv] of proj at qkv_off: causal convolution over `taps` tokens per channel
+ *                                  (conv_w [channels][taps], last column = current token; inputs before a portion come from its state row),
+ *                                  SiLU; q, k -> x * rsqrt(|x|^2 + unit_eps) per head, q also / sqrt(dim); beta = sigmoid(proj[b_off + h]),
+ *                                  decay = exp(-rate softplus(proj[a_off + h] + dt_bias[h])), rate = exp(a_log[h]); seq_of[t]: the portion of token t
+ *   ktb200_delta_scan              per portion seqs[0..3][s] and head: M <- a M; r = eta (v - M^T k); M <- M + k r^T; y = M^T q.
+ *                                  State rows: [M heads*dim*vdim | conv inputs (taps - 1)*channels] fp32, row stride state_stride; dim <= 256 */
+int ktb200_rope_norm_cache_write(const void* proj, long proj_stride, int q_off, int k_off, int v_off, int heads, int kv_heads, int dim, int vdim,
+                                 int rot_dims, int rot_layout, const double* inv_freq, int unit_rms, float eps, const void* v_other, long v_other_stride,
+                                 const float* blend, const int* pos, const int* slot, const int* page_table, int max_pages, int page_size, void* cache,
+                                 void* q_out, int n_tokens, int dtype, void* stream);
+size_t ktb200_window_softmax_attn_workspace(int n_tokens, int heads, int vdim, int splits);
+int ktb200_window_softmax_attn(const void* q, int heads, int kv_heads, int dim, int vdim, float scale, float softcap, int window, const int* pos,
+                               const int* slot, const int* page_table, int max_pages, int page_size, const void* cache, void* out, int n_tokens,
+                               int splits, float* workspace, int dtype, void* stream);
+int ktb200_delta_prep(const void* proj, long proj_stride, int qkv_off, int b_off, int a_off, const void* conv_w, int taps, const float* a_log,
+                      const float* dt_bias, int heads, int kv_heads, int dim, int vdim, float unit_eps, const int* seq_of, const int* seqs,
+                      int seqs_stride, float* state, long state_stride, float* qn, float* kn, float* vv, float* beta, float* decay, int n_tokens,
+                      int dtype, void* stream);
+int ktb200_delta_scan(const float* qn, const float* kn, const float* vv, const float* beta, const float* decay, int heads, int kv_heads, int dim,
+                      int vdim, const int* seqs, int seqs_stride, int n_seqs, float* state, long state_stride, float* o_out, void* stream);
 
 /* Diagnostics (bench.py --probe): time a plain read-only stream over `bytes` of device memory.
  * mode 0 = grid-stride coalesced 16-byte loads; mode 1 = every warp reads chunk_bytes pieces at hashed offsets

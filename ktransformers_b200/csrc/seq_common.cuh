@@ -83,6 +83,23 @@ __device__ __forceinline__ float lane_dot(const float* __restrict__ w, const flo
     }
     return s;
 }
+// Rotary pairs over the first rot_dims columns of a vector.  layout 0: columns (2i, 2i + 1) pair up; layout 1: column i pairs with
+// column i + rot_dims / 2.  A pair (x, y) at position pos becomes (x c - y s, y c + x s) with (c, s) = (cos, sin) of pos * inv_freq[i]
+// (fp64 table and angle).  `rot_partner`: the column that column c (< rot_dims) turns with; `rot_turn`: the turned value of column c.
+constexpr int kRotInterleaved = 0, kRotHalves = 1;
+__device__ __forceinline__ int rot_partner(int c, int rot_dims, int layout) {
+    const int half = rot_dims >> 1;
+    return layout == kRotHalves ? (c < half ? c + half : c - half) : (c ^ 1);
+}
+__device__ __forceinline__ float rot_turn(float own, float other, int c, int rot_dims, int layout, int pos, const double* __restrict__ inv_freq) {
+    const int half = rot_dims >> 1;
+    const bool second = layout == kRotHalves ? c >= half : (c & 1);
+    const int i = layout == kRotHalves ? (second ? c - half : c) : (c >> 1);
+    double sn, cs;
+    sincos((double)pos * inv_freq[i], &sn, &cs);
+    return second ? own * (float)cs + other * (float)sn : own * (float)cs - other * (float)sn;
+}
+
 template <typename T> __device__ __forceinline__ bool rows_vectorise(const T* base, int n) {
     return (n * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
 }

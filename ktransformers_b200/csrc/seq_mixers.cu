@@ -1,8 +1,9 @@
 // Token-major operators of decoder layers with norms on both sides of every sublayer, sigmoid (un-normalised) attention with
 // a distance bias, and gated linear attention with a recurrent state (libktb200_seq.so).
 //
-//   ktb200_group_rmsnorm_sandwich  x_out = x_in + gnorm(y) * w_post + row   then   h = gnorm(x_out) * w_pre
-//                                  (gnorm: RMS norm in `groups` equal consecutive parts; every term optional)
+//   ktb200_group_rmsnorm_sandwich  x_out = x_in + gnorm(y) * (w_post + c) + row   then   h = gnorm(x_out) * (w_pre + c)
+//                                  (gnorm: RMS norm in `groups` equal consecutive parts; every term optional; c = 0, or 1 for
+//                                  zero-centred weights; without w_pre, h is x_out rounded to the compute dtype)
 //   ktb200_qk_norm_cache_write     per-head RMS norm of queries and keys, query temperature by position, paged write of [k | v]
 //   ktb200_sigmoid_bias_attn       o_i = sum_{j <= i} sigmoid(scale q_i.k_j + bias[h][min(i - j, n - 1)] + pb[h]) v_j over the paged
 //                                  cache, grouped query heads, times sigmoid(gate[i][h]); key range cut into splits for few tokens;
@@ -11,6 +12,7 @@
 //                                  a_t = sigmoid(z_t + b)^(1/tau)
 //   ktb200_gla_out                 per-head RMS norm of o times silu(gate)
 //   ktb200_xielu                   z > 0: sp(p) z^2 + z/2 ;  z <= 0: (1/2 + sp(q)) (exp(z) - 1 - z) + z/2 ,  sp = softplus
+//   ktb200_gated_act_mul           act(gate) * up over rows [gate | up], act = SiLU or the tanh form of GELU
 //
 // Storage type T (bf16 or float) for activations, weights and cache rows; every sum, norm, score, weight, decay and state is
 // fp32.  Rows are addressed through per-token / per-sequence index arrays: one launch serves a ragged batch.
@@ -33,7 +35,7 @@ __device__ __forceinline__ void prefetch_l2_line(const void* p) { asm volatile("
 template <typename T>
 __global__ void __launch_bounds__(256) sandwich_norm_kernel(const float* __restrict__ x_in, const void* __restrict__ y, int y_type, const T* __restrict__ w_post,
                                                             const float* __restrict__ row_add, float* __restrict__ x_out, const T* __restrict__ w_pre,
-                                                            T* __restrict__ h_out, int groups, float eps, int D, int stash) {
+                                                            T* __restrict__ h_out, int groups, float eps, int D, int stash, float w_off) {
     extern __shared__ __align__(16) float sm[];
     float* red = sm;
     float* row = sm + 32;
@@ -71,10 +73,11 @@ __global__ void __launch_bounds__(256) sandwich_norm_kernel(const float* __restr
         float s2 = 0.f;
         for (int i = lane * 4; i < chunk; i += 128) {
             float4 v = load4(row + lo + i);
-            if (w_post) { const float4 w = load4(w_post + lo + i); v.x = v.x * inv * w.x; v.y = v.y * inv * w.y; v.z = v.z * inv * w.z; v.w = v.w * inv * w.w; }
+            if (w_post) { const float4 w = load4(w_post + lo + i); v.x = v.x * inv * (w.x + w_off); v.y = v.y * inv * (w.y + w_off); v.z = v.z * inv * (w.z + w_off); v.w = v.w * inv * (w.w + w_off); }
             if (x_in) { const float4 u = load4(x_in + t * D + lo + i); v.x = u.x + v.x; v.y = u.y + v.y; v.z = u.z + v.z; v.w = u.w + v.w; }
             if (row_add) { const float4 u = load4(row_add + lo + i); v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w; }
             if (x_out) store4(x_out + t * D + lo + i, v);
+            if (h_out && !w_pre) store4(h_out + t * D + lo + i, v);      // the next sublayer reads the residual itself
             store4(row + lo + i, v);
             s2 += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
         }
@@ -88,7 +91,7 @@ __global__ void __launch_bounds__(256) sandwich_norm_kernel(const float* __restr
             for (int i = lane * 4; i < chunk; i += 128) {
                 float4 v = load4(row + lo + i);
                 const float4 w = load4(w_pre + lo + i);
-                v.x = v.x * inv2 * w.x; v.y = v.y * inv2 * w.y; v.z = v.z * inv2 * w.z; v.w = v.w * inv2 * w.w;
+                v.x = v.x * inv2 * (w.x + w_off); v.y = v.y * inv2 * (w.y + w_off); v.z = v.z * inv2 * (w.z + w_off); v.w = v.w * inv2 * (w.w + w_off);
                 store4(h_out + t * D + lo + i, v);
             }
         }
@@ -114,10 +117,11 @@ __global__ void __launch_bounds__(256) sandwich_norm_kernel(const float* __restr
         for (int i = tid; i < gs; i += blockDim.x) {
             const long at = t * D + lo + i;
             float v = load_hidden(y, at, y_type);
-            if (w_post) v = v * inv * to_f(w_post[lo + i]);
+            if (w_post) v = v * inv * (to_f(w_post[lo + i]) + w_off);
             if (x_in) v = x_in[at] + v;
             if (row_add) v += row_add[lo + i];
             if (x_out) x_out[at] = v;
+            if (h_out && !w_pre) h_out[at] = from_f<T>(v);
             if (stash) row[lo + i] = v;
             s2 += v * v;
         }
@@ -126,7 +130,7 @@ __global__ void __launch_bounds__(256) sandwich_norm_kernel(const float* __restr
             const float inv2 = 1.0f / sqrtf(s2 / (float)gs + eps);
             for (int i = tid; i < gs; i += blockDim.x) {      // the same thread wrote these values
                 const float v = stash ? row[lo + i] : x_out[t * D + lo + i];
-                h_out[t * D + lo + i] = from_f<T>(v * inv2 * to_f(w_pre[lo + i]));
+                h_out[t * D + lo + i] = from_f<T>(v * inv2 * (to_f(w_pre[lo + i]) + w_off));
             }
         }
     }
@@ -605,6 +609,20 @@ __global__ void xielu_kernel(const T* __restrict__ z, T* __restrict__ out, const
     }
 }
 
+// ------------------------------------------------------------------------------------------------ gated activation
+// out[t][i] = act(gu[t][i]) * gu[t][F + i] for rows [gate F | up F]; act 0: SiLU, 1: the tanh form of GELU
+__device__ __forceinline__ float act_gelu_tanh(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+template <typename T>
+__global__ void gated_act_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long n_rows, int F, int act) {
+    const long n = n_rows * F;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const long t = i / F;
+        const int c = (int)(i - t * F);
+        const float g = to_f(gu[t * 2 * F + c]), u = to_f(gu[t * 2 * F + F + c]);
+        out[i] = from_f<T>((act == 1 ? act_gelu_tanh(g) : act_silu(g)) * u);
+    }
+}
+
 }  // namespace ktb
 
 using namespace ktb;
@@ -627,9 +645,9 @@ static int grid_for(long n, int per_block) {
 }
 
 extern "C" int ktb200_group_rmsnorm_sandwich(const float* x_in, const void* y, int y_type, const void* w_post, const float* row_add, float* x_out, const void* w_pre,
-                                             void* h_out, int groups, float eps, int n_tokens, int width, int dtype, void* stream) {
+                                             void* h_out, int groups, float eps, float weight_offset, int n_tokens, int width, int dtype, void* stream) {
     if (n_tokens <= 0) return KTB200_OK;
-    if (!y || groups <= 0 || width <= 0 || width % groups || (w_pre && !h_out) || (!x_out && !w_pre) || (y_type != KTB200_TYPE_BF16 && y_type != KTB200_TYPE_F32)) {
+    if (!y || groups <= 0 || width <= 0 || width % groups || (w_pre && !h_out) || (!x_out && !h_out) || (y_type != KTB200_TYPE_BF16 && y_type != KTB200_TYPE_F32)) {
         set_error("group_rmsnorm_sandwich: bad argument");
         return KTB200_EINVAL;
     }
@@ -638,7 +656,7 @@ extern "C" int ktb200_group_rmsnorm_sandwich(const float* x_in, const void* y, i
     const size_t smem = (32 + (stash ? (size_t)width : 0)) * sizeof(float);
     SEQ_DISPATCH(dtype, {
         GRANT_SMEM(sandwich_norm_kernel<T>, smem);
-        sandwich_norm_kernel<T><<<n_tokens, 256, smem, (cudaStream_t)stream>>>(x_in, y, y_type, (const T*)w_post, row_add, x_out, (const T*)w_pre, (T*)h_out, groups, eps, width, stash);
+        sandwich_norm_kernel<T><<<n_tokens, 256, smem, (cudaStream_t)stream>>>(x_in, y, y_type, (const T*)w_post, row_add, x_out, (const T*)w_pre, (T*)h_out, groups, eps, width, stash, weight_offset);
     });
     KTB_LAUNCH_CHECK();
     return KTB200_OK;
@@ -769,6 +787,14 @@ extern "C" int ktb200_xielu(const void* z, void* out, const float* pq, long n, i
     if (!z || !out || !pq) { set_error("xielu: bad argument"); return KTB200_EINVAL; }
     if (n <= 0) return KTB200_OK;
     SEQ_DISPATCH(dtype, (xielu_kernel<T><<<grid_for(n, 256 * 4), 256, 0, (cudaStream_t)stream>>>((const T*)z, (T*)out, pq, n)));
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+extern "C" int ktb200_gated_act_mul(const void* gate_up, void* out, int n_tokens, int ff, int act, int dtype, void* stream) {
+    if (!gate_up || !out || ff <= 0 || (act != 0 && act != 1)) { set_error("gated_act_mul: bad argument"); return KTB200_EINVAL; }
+    if (n_tokens <= 0) return KTB200_OK;
+    SEQ_DISPATCH(dtype, (gated_act_mul_kernel<T><<<grid_for((long)n_tokens * ff, 256 * 4), 256, 0, (cudaStream_t)stream>>>((const T*)gate_up, (T*)out, n_tokens, ff, act)));
     KTB_LAUNCH_CHECK();
     return KTB200_OK;
 }

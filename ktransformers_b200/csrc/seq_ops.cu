@@ -192,7 +192,7 @@ __global__ void __launch_bounds__(256) group_norm_shift_kernel(const float* __re
 // ------------------------------------------------------------------------------------------------ latent prep
 // One CTA per token.  proj row = [ q latent (q_rank) | kv latent (kv_rank) | rotated key part (rot_dim) | ... ].
 template <typename T>
-__global__ void __launch_bounds__(256) latent_prep_kernel(const T* __restrict__ proj, long proj_stride, int q_rank, int kv_rank, int rot_dim, int rot_dims,
+__global__ void __launch_bounds__(256) latent_prep_kernel(const T* __restrict__ proj, long proj_stride, int q_rank, int kv_rank, int rot_dim, int rot_dims, int rot_layout,
                                                           const double* __restrict__ inv_freq, const T* __restrict__ qn_w, const T* __restrict__ kvn_w, float eps,
                                                           const int* __restrict__ pos, const int* __restrict__ slot, const int* __restrict__ page_table, int max_pages,
                                                           int page_size, T* __restrict__ cache, T* __restrict__ cq_out) {
@@ -214,20 +214,15 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(const T* __restrict__ 
     const T* kr = p + q_rank + kv_rank;
     for (int i = tid; i < rot_dim; i += blockDim.x) {
         float v = to_f(kr[i]);
-        if (i < rot_dims) {
-            double sn, cs;
-            sincos((double)ps * inv_freq[i >> 1], &sn, &cs);
-            const float other = to_f(kr[i ^ 1]);
-            v = (i & 1) ? v * (float)cs + other * (float)sn : v * (float)cs - other * (float)sn;
-        }
+        if (i < rot_dims) v = rot_turn(v, to_f(kr[rot_partner(i, rot_dims, rot_layout)]), i, rot_dims, rot_layout, ps, inv_freq);
         c[kv_rank + i] = from_f<T>(v);
     }
 }
 
 // ------------------------------------------------------------------------------------------------ rotated query part
-// out[t][h][:] = rot(q[t][h][dn : dn + dr]) at position pos[t] (interleaved pairs over the first rot_dims columns)
+// out[t][h][:] = rot(q[t][h][dn : dn + dr]) at position pos[t] (pairs of either layout over the first rot_dims columns)
 template <typename T>
-__global__ void rope_rows_kernel(const T* __restrict__ q, int H, int dn, int dr, int rot_dims, const double* __restrict__ inv_freq, const int* __restrict__ pos,
+__global__ void rope_rows_kernel(const T* __restrict__ q, int H, int dn, int dr, int rot_dims, int rot_layout, const double* __restrict__ inv_freq, const int* __restrict__ pos,
                                  T* __restrict__ out, int n_tokens) {
     const long n = (long)n_tokens * H * dr;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
@@ -235,12 +230,7 @@ __global__ void rope_rows_kernel(const T* __restrict__ q, int H, int dn, int dr,
         const long th = i / dr;
         const T* src = q + th * (dn + dr) + dn;
         float v = to_f(src[d]);
-        if (d < rot_dims) {
-            double sn, cs;
-            sincos((double)pos[th / H] * inv_freq[d >> 1], &sn, &cs);
-            const float other = to_f(src[d ^ 1]);
-            v = (d & 1) ? v * (float)cs + other * (float)sn : v * (float)cs - other * (float)sn;
-        }
+        if (d < rot_dims) v = rot_turn(v, to_f(src[rot_partner(d, rot_dims, rot_layout)]), d, rot_dims, rot_layout, pos[th / H], inv_freq);
         out[i] = from_f<T>(v);
     }
 }
@@ -607,31 +597,33 @@ extern "C" int ktb200_group_rmsnorm_shift(const float* x_in, const void* delta_a
     return KTB200_OK;
 }
 
-extern "C" int ktb200_latent_prep(const void* proj, long proj_stride, int q_rank, int kv_rank, int rot_dim, int rot_dims, const double* inv_freq, const void* q_norm_w,
+extern "C" int ktb200_latent_prep(const void* proj, long proj_stride, int q_rank, int kv_rank, int rot_dim, int rot_dims, int rot_layout, const double* inv_freq, const void* q_norm_w,
                                   const void* kv_norm_w, float eps, const int* pos, const int* slot, const int* page_table, int max_pages, int page_size, void* cache,
                                   void* cq_out, int n_tokens, int dtype, void* stream) {
     if (!proj || !kv_norm_w || !pos || !slot || !page_table || !cache || kv_rank <= 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1) || q_rank < 0 ||
+        (rot_layout != kRotInterleaved && rot_layout != kRotHalves) ||
         (q_rank && (!q_norm_w || !cq_out)) || (rot_dims && !inv_freq) || page_size <= 0 || max_pages <= 0) {
         set_error("latent_prep: bad argument");
         return KTB200_EINVAL;
     }
     if (n_tokens <= 0) return KTB200_OK;
-    SEQ_DISPATCH(dtype, (latent_prep_kernel<T><<<n_tokens, 256, 0, (cudaStream_t)stream>>>((const T*)proj, proj_stride, q_rank, kv_rank, rot_dim, rot_dims, inv_freq, (const T*)q_norm_w,
+    SEQ_DISPATCH(dtype, (latent_prep_kernel<T><<<n_tokens, 256, 0, (cudaStream_t)stream>>>((const T*)proj, proj_stride, q_rank, kv_rank, rot_dim, rot_dims, rot_layout, inv_freq, (const T*)q_norm_w,
                                                                                            (const T*)kv_norm_w, eps, pos, slot, page_table, max_pages, page_size, (T*)cache, (T*)cq_out)));
     KTB_LAUNCH_CHECK();
     return KTB200_OK;
 }
 
-extern "C" int ktb200_rope_rows(const void* q, int num_heads, int dim, int rot_dim, int rot_dims, const double* inv_freq, const int* pos, void* out, int n_tokens, int dtype,
+extern "C" int ktb200_rope_rows(const void* q, int num_heads, int dim, int rot_dim, int rot_dims, int rot_layout, const double* inv_freq, const int* pos, void* out, int n_tokens, int dtype,
                                 void* stream) {
-    if (!q || !pos || !out || num_heads <= 0 || dim < 0 || rot_dim <= 0 || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1) || (rot_dims && !inv_freq)) {
+    if (!q || !pos || !out || num_heads <= 0 || dim < 0 || rot_dim <= 0 || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1) || (rot_dims && !inv_freq) ||
+        (rot_layout != kRotInterleaved && rot_layout != kRotHalves)) {
         set_error("rope_rows: bad argument");
         return KTB200_EINVAL;
     }
     if (n_tokens <= 0) return KTB200_OK;
     const long n = (long)n_tokens * num_heads * rot_dim;
     const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-    SEQ_DISPATCH(dtype, (rope_rows_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((const T*)q, num_heads, dim, rot_dim, rot_dims, inv_freq, pos, (T*)out, n_tokens)));
+    SEQ_DISPATCH(dtype, (rope_rows_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((const T*)q, num_heads, dim, rot_dim, rot_dims, rot_layout, inv_freq, pos, (T*)out, n_tokens)));
     KTB_LAUNCH_CHECK();
     return KTB200_OK;
 }

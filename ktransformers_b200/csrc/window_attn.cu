@@ -14,7 +14,7 @@
 // latent_window_attn_split    decode-sized batches with long windows: the key range of a (token, head group) is cut into
 //                             `splits` parts, each CTA writes (max, sum, un-normalised sum of latents); latent_window_merge
 //                             folds the parts and the sink.
-// The rotation of the query's rotated part (interleaved pairs, fp64 angle tables) happens in the prologue.
+// The rotation of the query's rotated part (pairs of either layout, fp64 angle tables) happens in the prologue.
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -33,7 +33,7 @@ struct WinAttnParams {
     const void* cache;    // [pages][page_size][R + dr]
     void* out;            // [T][H][R]
     float* part;          // split path: [T][H][splits][R + 2]
-    int T, H, dn, dr, R, rot_dims, window, max_pages, page_size, row_pad, splits;
+    int T, H, dn, dr, R, rot_dims, rot_layout, window, max_pages, page_size, row_pad, splits;
     float scale;
 };
 
@@ -64,12 +64,7 @@ __global__ void __launch_bounds__(kWinWarps * 32) latent_window_attn_kernel(cons
         const T* q = reinterpret_cast<const T*>(p.q) + ((long)t * p.H + h) * (p.dn + dr) + p.dn;
         for (int i = lane; i < dr; i += 32) {
             float v = to_f(q[i]);
-            if (i < p.rot_dims) {
-                double sn, cs;
-                sincos((double)pos * p.inv_freq[i >> 1], &sn, &cs);
-                const float other = to_f(q[i ^ 1]);
-                v = (i & 1) ? v * (float)cs + other * (float)sn : v * (float)cs - other * (float)sn;
-            }
+            if (i < p.rot_dims) v = rot_turn(v, to_f(q[rot_partner(i, p.rot_dims, p.rot_layout)]), i, p.rot_dims, p.rot_layout, pos, p.inv_freq);
             qr[warp * dr + i] = v;
         }
         const T* a = reinterpret_cast<const T*>(p.q_abs) + ((long)t * p.H + h) * R;
@@ -252,11 +247,11 @@ extern "C" size_t ktb200_latent_window_attn_workspace(int n_tokens, int num_head
     return splits > 1 ? (size_t)n_tokens * num_heads * splits * (kv_rank + 2) * sizeof(float) : 0;
 }
 
-extern "C" int ktb200_latent_window_attn(const void* q, const void* q_abs, int num_heads, int dim, int rot_dim, int kv_rank, int rot_dims, const double* inv_freq, float scale,
+extern "C" int ktb200_latent_window_attn(const void* q, const void* q_abs, int num_heads, int dim, int rot_dim, int kv_rank, int rot_dims, int rot_layout, const double* inv_freq, float scale,
                                          const float* sink, int window, const int* pos, const int* slot, const int* page_table, int max_pages, int page_size, const void* cache,
                                          void* out, int n_tokens, int splits, void* workspace, int dtype, void* stream) {
     if (!q || !q_abs || !pos || !slot || !page_table || !cache || !out || num_heads <= 0 || dim < 0 || rot_dim < 0 || kv_rank <= 0 || kv_rank > 1024 || rot_dims < 0 ||
-        rot_dims > rot_dim || (rot_dims & 1) || (rot_dims && !inv_freq) || max_pages <= 0 || page_size <= 0 || (splits > 1 && !workspace) || splits > 64) {
+        rot_dims > rot_dim || (rot_dims & 1) || (rot_dims && !inv_freq) || (rot_layout != kRotInterleaved && rot_layout != kRotHalves) || max_pages <= 0 || page_size <= 0 || (splits > 1 && !workspace) || splits > 64) {
         set_error("latent_window_attn: bad argument (latent size <= 1024)");
         return KTB200_EINVAL;
     }
@@ -267,7 +262,7 @@ extern "C" int ktb200_latent_window_attn(const void* q, const void* q_abs, int n
     while (((RS + pad) * esz) % 4 != 0 || (((RS + pad) * esz) / 4) % 2 == 0) pad++;
     const size_t smem = (size_t)kWinWarps * (kv_rank + rot_dim + kWinTile) * sizeof(float) + (size_t)kWinTile * (RS + pad) * esz;
     if (smem > 227 * 1024) { set_error("latent_window_attn: tile does not fit shared memory"); return KTB200_EINVAL; }
-    WinAttnParams p{q, q_abs, inv_freq, sink, pos, slot, page_table, cache, out, (float*)workspace, n_tokens, num_heads, dim, rot_dim, kv_rank, rot_dims, window, max_pages,
+    WinAttnParams p{q, q_abs, inv_freq, sink, pos, slot, page_table, cache, out, (float*)workspace, n_tokens, num_heads, dim, rot_dim, kv_rank, rot_dims, rot_layout, window, max_pages,
                     page_size, pad, splits > 1 ? splits : 1, scale};
     if (dtype == KTB200_TYPE_BF16) return launch_win_t<__nv_bfloat16>(p, smem, (cudaStream_t)stream);
     if (dtype == KTB200_TYPE_F32) return launch_win_t<float>(p, smem, (cudaStream_t)stream);

@@ -12,7 +12,19 @@ from typing import List, Optional
 @dataclass
 class RotarySpec:
     base: float
-    dims: int                      # leading dimensions of the rotated part that are actually turned (interleaved pairs)
+    dims: int                      # leading dimensions of the rotated part that are actually turned
+    layout: str = "interleaved"    # "interleaved": columns 2i and 2i + 1 turn together; "halves": column i with column i + dims / 2
+    factor: float = 1.0            # linear scaling: every frequency is divided by this
+
+    def inv_freq(self, device):
+        """base^(-2 i / dims) / factor for the dims / 2 pairs, float64 (the kernels take the angle in fp64)"""
+        import torch
+        i = torch.arange(self.dims // 2, dtype=torch.float64)
+        return (float(self.base) ** (-2.0 * i / max(self.dims, 1)) / float(self.factor)).to(device)
+
+    @property
+    def layout_code(self) -> int:
+        return {"interleaved": 0, "halves": 1}[self.layout]
 
 
 @dataclass
@@ -26,6 +38,15 @@ class LatentAttentionSpec:
     scale: float
     rot: RotarySpec
     window: Optional[int] = None   # query i sees keys j with 0 <= i - j < window; None: all earlier keys
+    sink: bool = True              # a value-less term exp(sink_h) in the soft-max denominator
+    gate: bool = True              # a sigmoid output gate read from the mixer's input
+    # q_rank = 0: the query is one full-rank projection of the mixer's input (no query latent, no norm)
+
+    def cache_row_width(self) -> int:
+        return self.kv_rank + self.rot_dim
+
+    def state_width(self) -> int:
+        return 0
 
     @classmethod
     def from_dict(cls, d: dict) -> "LatentAttentionSpec":

@@ -75,9 +75,12 @@ class ForwardBatch:
     `tokens`, `pos`, `slot` [T]; for layers that keep a previous-token row: `prev_idx` (row of the previous token inside this
     step or -1), `rd_row` / `wr_row` (state rows to read when the previous token came in an earlier step / to write for the
     last token of a sequence's portion; -1: none).  `seqs` [4, >= n_seqs]: the same per sequence portion, for layers whose
-    state is a recurrence over the portion's tokens.  `want` [W]: rows whose logits the caller asked for."""
+    state is a recurrence over the portion's tokens, and `seq_of` [T]: the portion a token belongs to (column of `seqs`), for
+    layers that look further back than one token.  `want` [W]: rows whose logits the caller asked for."""
 
-    __slots__ = ("tokens", "pos", "slot", "prev_idx", "rd_row", "wr_row", "want", "n_tokens", "max_kv", "seqs", "n_seqs")
+    N_META = 10      # index rows per token: pos, slot, prev_idx, rd_row, wr_row, the four rows of `seqs`, seq_of
+
+    __slots__ = ("tokens", "pos", "slot", "prev_idx", "rd_row", "wr_row", "want", "n_tokens", "max_kv", "seqs", "n_seqs", "seq_of")
 
     def __init__(self, meta: torch.Tensor, tokens: torch.Tensor, want: torch.Tensor, max_kv: int, n_seqs: int = 0):
         self.pos, self.slot, self.prev_idx, self.rd_row, self.wr_row = meta[0], meta[1], meta[2], meta[3], meta[4]
@@ -85,6 +88,7 @@ class ForwardBatch:
         # per sequence portion, for layers that carry a recurrent state: rows (first token's row, token count, state row to
         # read or -1, state row to write) in the first n_seqs columns
         self.seqs, self.n_seqs = (meta[5:9] if meta.shape[0] >= 9 else None), n_seqs
+        self.seq_of = meta[9] if meta.shape[0] >= 10 else None
 
 
 class PagedStateCache:
@@ -208,15 +212,16 @@ class PagedStateCache:
 
     def build_batch(self, entries, want_all: bool = False, static=None) -> ForwardBatch:
         """entries: [(seq_id, tokens, want)] — reserve pages, lay out the per-token index rows, one host-to-device copy.
-        `static` = (meta [9, T] int32, tokens [T] int64) device buffers of a captured step: the rows are copied into them and
+        `static` = (meta [ForwardBatch.N_META, T] int32, tokens [T] int64) device buffers of a captured step: the rows are copied into them and
         the batch is built on them, asking for every row (the caller picks the wanted ones from the captured output)."""
-        rows, toks, want, base, max_kv = [[], [], [], [], [], [], [], [], []], [], [], 0, 0
+        rows, toks, want, base, max_kv = [[] for _ in range(ForwardBatch.N_META)], [], [], 0, 0
         for seq_id, tokens, w in entries:
             s = self.open(seq_id)
             n = len(tokens)
             start = self.extend(s, n)
             rd, wr = self.state_rows(s, start)
-            for r, v in zip(rows[5:], (base, n, rd, wr)):
+            rows[9] += [len(rows[5])] * n
+            for r, v in zip(rows[5:9], (base, n, rd, wr)):
                 r.append(v)
             rows[0] += range(start, start + n)
             rows[1] += [s] * n
@@ -228,7 +233,7 @@ class PagedStateCache:
             base += n
             max_kv = max(max_kv, start + n)
         n_seqs = len(rows[5])
-        for r in rows[5:]:
+        for r in rows[5:9]:
             r += [0] * (base - n_seqs)
         self.sync_table()
         if static is not None:

@@ -108,12 +108,12 @@ SEQ_SYMBOLS = {
     "ktb200_launch_count": (C.c_ulonglong, []),
     "ktb200_moe_gate_forward": (_I, [C.POINTER(GateConfig), _I, _VP, _VP, _VP, _VP, _VP, _VP]),
     "ktb200_group_rmsnorm_shift": (_I, [_VP, _VP, _I, _VP, _I, _F, _VP, _VP, _I, _F, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
-    "ktb200_latent_prep": (_I, [_VP, _L, _I, _I, _I, _I, _VP, _VP, _VP, _F, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP]),
+    "ktb200_latent_prep": (_I, [_VP, _L, _I, _I, _I, _I, _I, _VP, _VP, _VP, _F, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP]),
     "ktb200_latent_window_attn_workspace": (C.c_size_t, [_I, _I, _I, _I]),
-    "ktb200_latent_window_attn": (_I, [_VP, _VP, _I, _I, _I, _I, _I, _VP, _F, _VP, _I, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP, _I, _VP]),
+    "ktb200_latent_window_attn": (_I, [_VP, _VP, _I, _I, _I, _I, _I, _I, _VP, _F, _VP, _I, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP, _I, _VP]),
     "ktb200_latent_window_attn_tc_workspace": (C.c_size_t, [_I, _I, _I, _I]),
     "ktb200_latent_window_attn_tc": (_I, [_VP, _VP, _I, _F, _VP, _I, _VP, _VP, _VP, _I, _I, _VP, _L, _VP, _I, _I, _VP, C.c_size_t, _VP]),
-    "ktb200_rope_rows": (_I, [_VP, _I, _I, _I, _I, _VP, _VP, _VP, _I, _I, _VP]),
+    "ktb200_rope_rows": (_I, [_VP, _I, _I, _I, _I, _I, _VP, _VP, _VP, _I, _I, _VP]),
     "ktb200_sigmoid_gate_mul": (_I, [_VP, _VP, _L, _VP, _I, _I, _I, _I, _VP]),
     "ktb200_poly_norm": (_I, [_VP, _VP, _VP, _F, _I, _I, _I, _VP]),
     "ktb200_experts_gate_up": (_I, [_VP, _VP, _I, _VP, _VP, _VP, _I, _I, _I, _I, _VP]),
@@ -121,7 +121,7 @@ SEQ_SYMBOLS = {
     "ktb200_experts_gate_up_by_expert": (_I, [_VP, _VP, _I, _I, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
     "ktb200_experts_down_by_expert": (_I, [_VP, _VP, _VP, _I, _I, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
     # csrc/seq_mixers.cu
-    "ktb200_group_rmsnorm_sandwich": (_I, [_VP, _VP, _I, _VP, _VP, _VP, _VP, _VP, _I, _F, _I, _I, _I, _VP]),
+    "ktb200_group_rmsnorm_sandwich": (_I, [_VP, _VP, _I, _VP, _VP, _VP, _VP, _VP, _I, _F, _F, _I, _I, _I, _VP]),
     "ktb200_qk_norm_cache_write": (_I, [_VP, _L, _I, _I, _I, _I, _VP, _VP, _F, _F, _I, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP]),
     "ktb200_sigmoid_bias_attn_workspace": (C.c_size_t, [_I, _I, _I, _I]),
     "ktb200_sigmoid_bias_attn": (_I, [_VP, _I, _I, _I, _I, _F, _VP, _I, _VP, _VP, _VP, _VP, _I, _I, _VP, _I, _I, _VP, _VP, _L, _VP, _I, _I, _VP, _I, _I, _VP]),
@@ -130,6 +130,13 @@ SEQ_SYMBOLS = {
     "ktb200_gla_scan": (_I, [_VP, _L, _I, _I, _I, _VP, _L, _VP, _F, _I, _I, _I, _VP, _I, _I, _I, _VP, _VP, _I, _VP]),
     "ktb200_gla_out": (_I, [_VP, _VP, _F, _VP, _L, _VP, _I, _I, _I, _I, _VP]),
     "ktb200_xielu": (_I, [_VP, _VP, _VP, _L, _I, _VP]),
+    "ktb200_gated_act_mul": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
+    # csrc/softmax_attn.cu, csrc/delta_rule.cu
+    "ktb200_rope_norm_cache_write": (_I, [_VP, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _VP, _I, _F, _VP, _L, _VP, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP]),
+    "ktb200_window_softmax_attn_workspace": (C.c_size_t, [_I, _I, _I, _I]),
+    "ktb200_window_softmax_attn": (_I, [_VP, _I, _I, _I, _I, _F, _F, _I, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP, _I, _VP]),
+    "ktb200_delta_prep": (_I, [_VP, _L, _I, _I, _I, _VP, _I, _VP, _VP, _I, _I, _I, _I, _F, _VP, _VP, _I, _VP, _L, _VP, _VP, _VP, _VP, _VP, _I, _I, _VP]),
+    "ktb200_delta_scan": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP, _I, _I, _VP, _L, _VP, _VP]),
 }
 SEQ_LIB_PATH = os.path.join(_HERE, "libktb200_seq.so")
 _seq_lib = None
@@ -176,7 +183,7 @@ def lib() -> C.CDLL:
 
 
 def build_seq(verbose: bool = False) -> str:
-    """Compile libktb200_seq.so alone (four small sources, seconds).  Serialised across processes by a lock file."""
+    """Compile libktb200_seq.so alone (a handful of small sources, seconds).  Serialised across processes by a lock file."""
     import fcntl
     out = None if verbose else subprocess.DEVNULL
     os.makedirs(os.path.join(CSRC, "build"), exist_ok=True)

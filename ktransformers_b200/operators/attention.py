@@ -98,6 +98,8 @@ class KDeepseekV2Attention(BaseInjectedModule, DeepseekV3Attention):
 class KLatentWindowAttention(torch.nn.Module):
     """Latent attention with a low-rank query, a sliding window, a soft-max sink and a sigmoid output gate, run absorbed over
     the paged latent cache — the same formulation KDeepseekV2Attention uses for decode, here for prompt portions as well.
+    Each of the four is optional (`q_rank = 0`: the query is one full-rank projection `W_q`; `window = None`; `sink` /
+    `gate = False`), and the rotation pairs columns in either layout (`rot.layout`).
 
         P        = [W_dq ; W_dkv ; W_g] hs                      one GEMM over the three matrices that read the mixer input
         cq, c, k_r -> cache                                      ktb200_latent_prep (two RMS norms, rotation, paged write)
@@ -123,26 +125,29 @@ class KLatentWindowAttention(torch.nn.Module):
         P = lambda *shape, dt=dtype: torch.nn.Parameter(torch.empty(shape, dtype=dt, device=device), requires_grad=False)
         s = self.spec = spec
         self.width, self.eps, self.layer_idx = width, eps, layer_idx
-        self.n_in = s.q_rank + s.kv_rank + s.rot_dim + s.heads * s.vdim
+        # rows of the one matrix that reads the mixer input: [query latent, or the whole query when there is none | kv latent | rotated key part | gate]
+        self.n_q = s.q_rank if s.q_rank else s.heads * (s.dim + s.rot_dim)
+        self.n_in = self.n_q + s.kv_rank + s.rot_dim + (s.heads * s.vdim if s.gate else 0)
         self.w_in = P(self.n_in, width)
-        self.q_norm, self.kv_norm = P(s.q_rank), P(s.kv_rank)
-        self.uq = P(s.heads * (s.dim + s.rot_dim), s.q_rank)
+        self.q_norm, self.kv_norm = (P(s.q_rank) if s.q_rank else None), P(s.kv_rank)
+        self.uq = P(s.heads * (s.dim + s.rot_dim), s.q_rank) if s.q_rank else None
         self.w_uk = P(s.heads, s.dim, s.kv_rank)
         self.w_uv_t = P(s.heads, s.kv_rank, s.vdim)
-        self.sink = P(s.heads, dt=torch.float32)
+        self.sink = P(s.heads, dt=torch.float32) if s.sink else None
         self.o = P(width, s.heads * s.vdim)
-        i = torch.arange(s.rot.dims // 2, dtype=torch.float64)
-        self.register_buffer("inv_freq", (float(s.rot.base) ** (-2.0 * i / max(s.rot.dims, 1))).to(device), persistent=False)
+        self.register_buffer("inv_freq", s.rot.inv_freq(device), persistent=False)
 
     def load(self, loader, prefix: str):
         s, t = self.spec, lambda n: loader.load_tensor(prefix + n, "cpu")
-        self.w_in.data.copy_(torch.cat([t("dq"), t("dkv"), t("g")], 0))
-        self.q_norm.data.copy_(t("dq.norm"))
+        self.w_in.data.copy_(torch.cat([t("dq") if s.q_rank else t("q"), t("dkv")] + ([t("g")] if s.gate else []), 0))
+        if s.q_rank:
+            self.q_norm.data.copy_(t("dq.norm"))
+            self.uq.data.copy_(t("uq"))
         self.kv_norm.data.copy_(t("dkv.norm"))
-        self.uq.data.copy_(t("uq"))
         self.w_uk.data.copy_(t("uk").view(s.heads, s.dim, s.kv_rank))
         self.w_uv_t.data.copy_(t("uv").view(s.heads, s.vdim, s.kv_rank).transpose(1, 2))
-        self.sink.data.copy_(t("sink").float())
+        if s.sink:
+            self.sink.data.copy_(t("sink").float())
         self.o.data.copy_(t("o"))
 
     def pick_splits(self, n_tokens: int, max_kv: int) -> int:
@@ -154,16 +159,20 @@ class KLatentWindowAttention(torch.nn.Module):
             return 1
         return max(1, min(32, keys // 128, 296 // ctas))
 
-    def forward(self, hs: torch.Tensor, batch, cache) -> torch.Tensor:
+    def forward(self, hs: torch.Tensor, batch, cache, cache_idx: Optional[int] = None) -> torch.Tensor:
         s, T, dev, dt = self.spec, hs.shape[0], hs.device, hs.dtype
         lib, code, st = native.seq_lib(), native.GGML_BF16 if dt == torch.bfloat16 else native.GGML_F32, torch.cuda.current_stream(hs.device).cuda_stream
-        kv = cache.key_cache[self.layer_idx]
+        kv = cache.key_cache[self.layer_idx if cache_idx is None else cache_idx]
+        lay, sink = s.rot.layout_code, (self.sink.data_ptr() if self.sink is not None else None)
         proj = torch.nn.functional.linear(hs, self.w_in)
-        cq = torch.empty((T, s.q_rank), dtype=dt, device=dev)
-        native.check_seq(lib.ktb200_latent_prep(proj.data_ptr(), self.n_in, s.q_rank, s.kv_rank, s.rot_dim, s.rot.dims, self.inv_freq.data_ptr(), self.q_norm.data_ptr(),
-                                                self.kv_norm.data_ptr(), float(self.eps), batch.pos.data_ptr(), batch.slot.data_ptr(), cache.page_table.data_ptr(),
-                                                cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), cq.data_ptr(), T, code, st))
-        q = torch.nn.functional.linear(cq, self.uq)
+        cq = torch.empty((T, s.q_rank), dtype=dt, device=dev) if s.q_rank else None
+        # the prep kernel reads [query latent (q_rank) | kv latent | rotated key part] from its row pointer
+        lat_in = proj if s.q_rank else proj[:, self.n_q:]
+        native.check_seq(lib.ktb200_latent_prep(lat_in.data_ptr(), self.n_in, s.q_rank, s.kv_rank, s.rot_dim, s.rot.dims, lay, self.inv_freq.data_ptr(),
+                                                self.q_norm.data_ptr() if s.q_rank else None, self.kv_norm.data_ptr(), float(self.eps), batch.pos.data_ptr(),
+                                                batch.slot.data_ptr(), cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size, kv.data_ptr(),
+                                                cq.data_ptr() if s.q_rank else None, T, code, st))
+        q = torch.nn.functional.linear(cq, self.uq) if s.q_rank else proj[:, :self.n_q].contiguous()
         if s.dim:       # [H, T, R] out of the batched product, token-major for the attention kernels
             q_abs = torch.bmm(q.view(T, s.heads, s.dim + s.rot_dim)[:, :, : s.dim].transpose(0, 1), self.w_uk).transpose(0, 1).contiguous()
         else:
@@ -171,22 +180,25 @@ class KLatentWindowAttention(torch.nn.Module):
         lat = torch.empty((T, s.heads, s.kv_rank), dtype=dt, device=dev)
         if self.use_tensor_path and dt == torch.bfloat16 and s.kv_rank == 512 and s.rot_dim == 64 and cache.page_size % 32 == 0:
             q_rot = torch.empty((T, s.heads, s.rot_dim), dtype=dt, device=dev)
-            native.check_seq(lib.ktb200_rope_rows(q.data_ptr(), s.heads, s.dim, s.rot_dim, s.rot.dims, self.inv_freq.data_ptr(), batch.pos.data_ptr(), q_rot.data_ptr(), T, code, st))
+            native.check_seq(lib.ktb200_rope_rows(q.data_ptr(), s.heads, s.dim, s.rot_dim, s.rot.dims, lay, self.inv_freq.data_ptr(), batch.pos.data_ptr(), q_rot.data_ptr(), T, code, st))
             wsb = lib.ktb200_latent_window_attn_tc_workspace(T, s.heads, s.window or 0, batch.max_kv)
             ws = torch.empty(wsb // 4, dtype=torch.float32, device=dev)
-            native.check_seq(lib.ktb200_latent_window_attn_tc(q_abs.data_ptr(), q_rot.data_ptr(), s.heads, float(s.scale), self.sink.data_ptr(), s.window or 0, batch.pos.data_ptr(),
+            native.check_seq(lib.ktb200_latent_window_attn_tc(q_abs.data_ptr(), q_rot.data_ptr(), s.heads, float(s.scale), sink, s.window or 0, batch.pos.data_ptr(),
                                                               batch.slot.data_ptr(), cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size, kv.data_ptr(),
                                                               kv.shape[0] * kv.shape[1], lat.data_ptr(), T, batch.max_kv, ws.data_ptr(), wsb, st))
         else:
             splits = self.pick_splits(T, batch.max_kv)
             ws = torch.empty(lib.ktb200_latent_window_attn_workspace(T, s.heads, s.kv_rank, splits) // 4, dtype=torch.float32, device=dev) if splits > 1 else None
-            native.check_seq(lib.ktb200_latent_window_attn(q.data_ptr(), q_abs.data_ptr(), s.heads, s.dim, s.rot_dim, s.kv_rank, s.rot.dims, self.inv_freq.data_ptr(),
-                                                           float(s.scale), self.sink.data_ptr(), s.window or 0, batch.pos.data_ptr(), batch.slot.data_ptr(),
+            native.check_seq(lib.ktb200_latent_window_attn(q.data_ptr(), q_abs.data_ptr(), s.heads, s.dim, s.rot_dim, s.kv_rank, s.rot.dims, lay, self.inv_freq.data_ptr(),
+                                                           float(s.scale), sink, s.window or 0, batch.pos.data_ptr(), batch.slot.data_ptr(),
                                                            cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), lat.data_ptr(), T, splits,
                                                            ws.data_ptr() if ws is not None else None, code, st))
         o = torch.bmm(lat.transpose(0, 1), self.w_uv_t)
-        og = torch.empty((T, s.heads * s.vdim), dtype=dt, device=dev)
-        native.check_seq(lib.ktb200_sigmoid_gate_mul(o.data_ptr(), proj[:, s.q_rank + s.kv_rank + s.rot_dim:].data_ptr(), self.n_in, og.data_ptr(), T, s.heads, s.vdim, code, st))
+        if s.gate:
+            og = torch.empty((T, s.heads * s.vdim), dtype=dt, device=dev)
+            native.check_seq(lib.ktb200_sigmoid_gate_mul(o.data_ptr(), proj[:, self.n_q + s.kv_rank + s.rot_dim:].data_ptr(), self.n_in, og.data_ptr(), T, s.heads, s.vdim, code, st))
+        else:
+            og = o.transpose(0, 1).reshape(T, s.heads * s.vdim)
         return torch.nn.functional.linear(og, self.o)
 
 
@@ -292,3 +304,77 @@ class KSigmoidBiasAttention(torch.nn.Module):
                                                       cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), gate.data_ptr(), self.n_in,
                                                       o.data_ptr(), T, splits, ws.data_ptr() if ws is not None else None, code, int(tc), st))
         return torch.nn.functional.linear(o, self.o, self.o_b)
+
+
+class KCappedWindowAttention(torch.nn.Module):
+    """Causal soft-max attention over grouped key/value heads with biased projections, a partial rotation, unit-rms queries and
+    keys, capped scores, a sliding window, and values blended with another layer's values of the same token:
+
+        P       = [W_q ; W_k ; W_v] h + b                       one GEMM over the matrices that read the mixer input
+        q, k    = x / sqrt(mean(x^2) + eps) per head of rot(P[q]), rot(P[k])      (rotation over the first rot.dims columns,
+                                                                                   frequencies divided by rot.factor)
+        v       = (1 - t) P[v] + t v_other                      when `v_other` is handed in (t: one learned number)
+        [k | v] -> paged cache                                  ktb200_rope_norm_cache_write, all of the above in one launch
+        s_ij    = c tanh(scale q_i . k_j / c), c = softcap      for 0 <= i - j < window
+        o_i     = sum_j softmax_j(s_ij) v_j                     ktb200_window_softmax_attn (fp32 scores and weights)
+        out     = W_o o                                         GEMM
+
+    The blended v is what is cached.  `forward` also returns the layer's own values before the blend (a view of P), which the
+    model hands to later layers as their `v_other`.  Sizes, scale, cap, window, the rotation's constants and layout and the
+    unit-rms switch are constructor parameters (models/configuration_zivulix.CappedWindowAttentionSpec); `cache_idx` picks
+    the cache layer.  (The reference's attention operators: archive/ktransformers/operators/attention.py.)"""
+
+    def __init__(self, width: int, spec, eps: float, dtype=torch.bfloat16, device="cuda"):
+        super().__init__()
+        P = lambda *shape, dt=dtype: torch.nn.Parameter(torch.zeros(shape, dtype=dt, device=device), requires_grad=False)
+        s = self.spec = spec
+        if s.heads % s.kv_heads:
+            raise ValueError("query heads must divide into the key/value heads")
+        self.width, self.eps = width, eps
+        self.n_q, self.n_k, self.n_v = s.heads * s.dim, s.kv_heads * s.dim, s.kv_heads * s.vdim
+        self.n_in = (self.n_q + self.n_k + self.n_v + 7) // 8 * 8       # rows padded so that every row of P starts 16-byte aligned
+        self.w_in, self.b_in = P(self.n_in, width), P(self.n_in)
+        self.vmix = P(1, dt=torch.float32)
+        self.o = P(width, s.heads * s.vdim)
+        self.register_buffer("inv_freq", s.rot.inv_freq(device) if s.rot is not None and s.rot.dims else torch.zeros(1, dtype=torch.float64, device=device), persistent=False)
+
+    def load(self, loader, prefix: str):
+        t = lambda n: loader.load_tensor(prefix + n, "cpu")
+        rows = self.n_q + self.n_k + self.n_v
+        self.w_in.data[:rows].copy_(torch.cat([t("q"), t("k"), t("v")], 0))
+        self.b_in.data[:rows].copy_(torch.cat([t("q.b"), t("k.b"), t("v.b")], 0))
+        if self.spec.v_mix:
+            self.vmix.data.copy_(t("vmix").float().reshape(1))
+        self.o.data.copy_(t("o"))
+
+    def pick_splits(self, n_tokens: int, max_kv: int) -> int:
+        """Cut the key range when a small batch would leave most SMs idle on a long range."""
+        s = self.spec
+        keys = min(s.window, max_kv) if s.window else max_kv
+        ctas = n_tokens * s.kv_heads * ((s.heads // s.kv_heads + 7) // 8)
+        if ctas >= 148 or keys <= 256:
+            return 1
+        return max(1, min(64, keys // 128, 592 // ctas))
+
+    def forward(self, h: torch.Tensor, batch, cache, cache_idx: int, v_other: Optional[torch.Tensor] = None):
+        s, T, dev, dt = self.spec, h.shape[0], h.device, h.dtype
+        lib, code, st = native.seq_lib(), native.GGML_BF16 if dt == torch.bfloat16 else native.GGML_F32, torch.cuda.current_stream(h.device).cuda_stream
+        kv = cache.key_cache[cache_idx]
+        proj = torch.nn.functional.linear(h, self.w_in, self.b_in)
+        v_own = proj[:, self.n_q + self.n_k: self.n_q + self.n_k + self.n_v]
+        if v_other is not None and v_other.shape != v_own.shape:
+            raise ValueError("blended values must have this layer's key/value heads and value size")
+        q = torch.empty((T, s.heads, s.dim), dtype=dt, device=dev)
+        rot_dims = s.rot.dims if s.rot is not None else 0
+        native.check_seq(lib.ktb200_rope_norm_cache_write(proj.data_ptr(), self.n_in, 0, self.n_q, self.n_q + self.n_k, s.heads, s.kv_heads, s.dim, s.vdim, rot_dims,
+                                                          s.rot.layout_code if rot_dims else 0, self.inv_freq.data_ptr(), int(s.unit_rms), float(self.eps),
+                                                          v_other.data_ptr() if v_other is not None else None, v_other.stride(0) if v_other is not None else 0,
+                                                          self.vmix.data_ptr(), batch.pos.data_ptr(), batch.slot.data_ptr(), cache.page_table.data_ptr(),
+                                                          cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), q.data_ptr(), T, code, st))
+        o = torch.empty((T, s.heads * s.vdim), dtype=dt, device=dev)
+        splits = self.pick_splits(T, batch.max_kv)
+        ws = torch.empty(lib.ktb200_window_softmax_attn_workspace(T, s.heads, s.vdim, splits) // 4, dtype=torch.float32, device=dev) if splits > 1 else None
+        native.check_seq(lib.ktb200_window_softmax_attn(q.data_ptr(), s.heads, s.kv_heads, s.dim, s.vdim, float(s.scale), float(s.softcap or 0.0), int(s.window or 0),
+                                                        batch.pos.data_ptr(), batch.slot.data_ptr(), cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size,
+                                                        kv.data_ptr(), o.data_ptr(), T, splits, ws.data_ptr() if ws is not None else None, code, st))
+        return torch.nn.functional.linear(o, self.o), v_own

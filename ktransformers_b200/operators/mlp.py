@@ -62,3 +62,29 @@ class KXIELUMLP(nn.Module):
         native.check_seq(native.seq_lib().ktb200_xielu(z.data_ptr(), a.data_ptr(), self.pq.data_ptr(), z.numel(), GGML_OF[z.dtype],
                                                        torch.cuda.current_stream(z.device).cuda_stream))
         return F.linear(a, self.down)
+
+
+class KGatedMLP(nn.Module):
+    """A three-matrix gated feed-forward, W_down (act(W_gate h) * (W_up h)), act = "silu" or "gelu_tanh"
+    (u / 2 * (1 + tanh(0.7978845608 (u + 0.044715 u^3)))).  Gate and up are one stacked GEMM, the activation and the product one
+    `ktb200_gated_act_mul` launch (csrc/seq_mixers.cu, fp32 inside), down a GEMM.  (The reference's gated MLP:
+    modeling_deepseek_v3.py:385-397.)"""
+
+    ACTS = {"silu": 0, "gelu_tanh": 1}
+
+    def __init__(self, width: int, ff: int, act: str = "silu", dtype=torch.bfloat16, device="cuda"):
+        super().__init__()
+        self.width, self.ff, self.act = width, ff, self.ACTS[act]
+        self.gate_up = nn.Parameter(torch.empty((2 * ff, width), dtype=dtype, device=device), requires_grad=False)
+        self.down = nn.Parameter(torch.empty((width, ff), dtype=dtype, device=device), requires_grad=False)
+
+    def load(self, loader, prefix: str):
+        self.gate_up.data.copy_(torch.cat([loader.load_tensor(prefix + "gate", "cpu"), loader.load_tensor(prefix + "up", "cpu")], 0))
+        self.down.data.copy_(loader.load_tensor(prefix + "down", "cpu"))
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        gu = F.linear(h, self.gate_up)
+        a = torch.empty((h.shape[0], self.ff), dtype=gu.dtype, device=gu.device)
+        native.check_seq(native.seq_lib().ktb200_gated_act_mul(gu.data_ptr(), a.data_ptr(), gu.shape[0], self.ff, self.act, GGML_OF[gu.dtype],
+                                                               torch.cuda.current_stream(gu.device).cuda_stream))
+        return F.linear(a, self.down)

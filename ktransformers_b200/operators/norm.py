@@ -66,29 +66,36 @@ class KGroupRMSNorm(nn.Module):
         x_out = x_in + gnorm(y) * post.weight + row       the sublayer's output y normed and added to the fp32 residual
         h     = gnorm(x_out) * pre.weight                  the NEXT sublayer's input, rounded once to the compute dtype
 
-    with every term optional (no x_in / post: the stream restarts from y; no pre: nothing follows)."""
+    with every term optional (no x_in / post: the stream restarts from y; no pre: nothing follows, or with `cast_h` the next
+    sublayer reads the residual itself and h is x_out rounded to the compute dtype).  `weight_offset = 1`: the weight is
+    zero-centred and the row is scaled by 1 + weight (added in fp32 in the kernel)."""
 
-    def __init__(self, width: int, groups: int, eps: float, dtype=torch.bfloat16, device="cuda"):
+    def __init__(self, width: int, groups: int, eps: float, dtype=torch.bfloat16, device="cuda", weight_offset: float = 0.0):
         super().__init__()
         if width % groups:
             raise ValueError("the width must divide into the norm groups")
-        self.width, self.groups, self.eps = width, groups, eps
-        self.weight = nn.Parameter(torch.ones(width, dtype=dtype, device=device), requires_grad=False)
+        self.width, self.groups, self.eps, self.weight_offset = width, groups, eps, float(weight_offset)
+        self.weight = nn.Parameter(torch.full((width,), 1.0 - float(weight_offset), dtype=dtype, device=device), requires_grad=False)
 
     def load(self, loader, key: str):
         self.weight.data.copy_(loader.load_tensor(key, "cpu"))
 
     @staticmethod
     def fused(x_in: Optional[torch.Tensor], y: torch.Tensor, post: Optional["KGroupRMSNorm"], pre: Optional["KGroupRMSNorm"], row_add: Optional[torch.Tensor] = None,
-              keep_x: bool = True):
-        """x_in [T, width] fp32 or None, y [T, width] fp32 or the compute dtype.  Returns (x_out fp32 or None, h or None)."""
+              keep_x: bool = True, cast_h: bool = False):
+        """x_in [T, width] fp32 or None, y [T, width] fp32 or the compute dtype.  Returns (x_out fp32 or None, h or None); with
+        `cast_h` and no `pre`, h is x_out in the compute dtype (x_out itself when that is fp32)."""
         ref = pre if pre is not None else post
         T, D = y.shape
         assert y.is_contiguous() and (x_in is None or x_in.is_contiguous()) and D == ref.width
         dt = ref.weight.dtype
         x_out = torch.empty((T, D), dtype=torch.float32, device=y.device) if keep_x or pre is None else None
-        h = torch.empty((T, D), dtype=dt, device=y.device) if pre is not None else None
+        plain_h = cast_h and pre is None and dt != torch.float32
+        h = torch.empty((T, D), dtype=dt, device=y.device) if pre is not None or plain_h else None
         native.check_seq(native.seq_lib().ktb200_group_rmsnorm_sandwich(
             _ptr(x_in), y.data_ptr(), GGML_OF[y.dtype], post.weight.data_ptr() if post is not None else None, _ptr(row_add), _ptr(x_out),
-            pre.weight.data_ptr() if pre is not None else None, _ptr(h), ref.groups, float(ref.eps), T, D, GGML_OF[dt], torch.cuda.current_stream(y.device).cuda_stream))
+            pre.weight.data_ptr() if pre is not None else None, _ptr(h), ref.groups, float(ref.eps), float(ref.weight_offset), T, D, GGML_OF[dt],
+            torch.cuda.current_stream(y.device).cuda_stream))
+        if cast_h and pre is None and not plain_h:
+            h = x_out
         return x_out, h

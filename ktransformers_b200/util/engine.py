@@ -47,8 +47,9 @@ class _CapturedStep:
     """A decode step of a fixed batch size as a CUDA graph: static index / token buffers in, logits of every row out."""
 
     def __init__(self, model, cache, n: int):
+        from ..models.custom_cache import ForwardBatch
         dev = cache.device
-        self.meta = torch.zeros((9, n), dtype=torch.int32, device=dev)
+        self.meta = torch.zeros((ForwardBatch.N_META, n), dtype=torch.int32, device=dev)
         self.tokens = torch.zeros(n, dtype=torch.int64, device=dev)
         self.all_rows = torch.arange(n, dtype=torch.int64, device=dev)
         self.graph, self.logits = None, None
