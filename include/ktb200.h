@@ -465,8 +465,13 @@ int ktb200_rope_norm_cache_write(const void* proj, long proj_stride, int q_off, 
                                  void* q_out, int n_tokens, int dtype, void* stream);
 size_t ktb200_window_softmax_attn_workspace(int n_tokens, int heads, int vdim, int splits);
 int ktb200_window_softmax_attn(const void* q, int heads, int kv_heads, int dim, int vdim, float scale, float softcap, int window, const int* pos,
-                               const int* slot, const int* page_table, int max_pages, int page_size, const void* cache, void* out, int n_tokens,
-                               int splits, float* workspace, int dtype, void* stream);
+                               const int* slot, const int* seqs, int seqs_stride, int n_seqs, const int* page_table, int max_pages, int page_size,
+                               const void* cache, void* out, int n_tokens, int splits, float* workspace, int dtype, int allow_tensor_cores,
+                               void* stream);
+/* whether that call runs tensor-core tiles (bf16, dim and vdim multiples of 16 up to 128, seqs given), and an upper bound of its
+ * row tiles per key/value head (for choosing splits) */
+int ktb200_window_softmax_attn_uses_tensor_cores(int heads, int kv_heads, int dim, int vdim, int dtype);
+int ktb200_window_softmax_attn_tiles(int heads, int kv_heads, int n_tokens, int n_seqs);
 int ktb200_delta_prep(const void* proj, long proj_stride, int qkv_off, int b_off, int a_off, const void* conv_w, int taps, const float* a_log,
                       const float* dt_bias, int heads, int kv_heads, int dim, int vdim, float unit_eps, const int* seq_of, const int* seqs,
                       int seqs_stride, float* state, long state_stride, float* qn, float* kn, float* vv, float* beta, float* decay, int n_tokens,

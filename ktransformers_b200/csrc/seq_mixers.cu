@@ -20,6 +20,7 @@
 
 #include "common.cuh"
 #include "seq_common.cuh"
+#include "mma_tile.cuh"
 
 namespace ktb {
 
@@ -258,29 +259,6 @@ __global__ void __launch_bounds__(256) sigmoid_attn_kernel(const T* __restrict__
 // not normalised.  grid (tile bound, G * head blocks, splits); tiles are found from the per-sequence rows `seqs`.
 constexpr int kMmaRows = 64, kMmaKeys = 64, kMmaPad = 8;
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
-    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
-    const int sz = valid ? 16 : 0;      // 0: the 16 bytes are zero-filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sa), "l"(gmem), "r"(sz) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
-    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sa));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
-    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sa));
-}
-__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&v);
-}
 __device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 template <int D16MAX, int DV16MAX, int ROWS, int KEYS>
@@ -682,12 +660,6 @@ extern "C" size_t ktb200_sigmoid_bias_attn_workspace(int n_tokens, int heads, in
     return splits > 1 ? (size_t)splits * n_tokens * heads * vdim * sizeof(float) : 0;
 }
 
-// rows of query heads per tile of the tensor-core kernel: the whole group when it fits 16 rows, else its largest divisor that does
-static int mma_heads_per_tile(int group) {
-    for (int r = group < 16 ? group : 16; r > 1; r--)
-        if (group % r == 0) return r;
-    return 1;
-}
 extern "C" int ktb200_sigmoid_bias_attn_uses_tensor_cores(int heads, int kv_heads, int dim, int vdim, int dtype) {
     return dtype == KTB200_TYPE_BF16 && kv_heads > 0 && heads % kv_heads == 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 128 && vdim <= 128;
 }

@@ -6,7 +6,8 @@
 //                                  v <- (1 - t) v + t v_other with one learned t (optional); [k | v] into the paged cache, q into q_out
 //   ktb200_window_softmax_attn     o_i = sum_j softmax_j(cap(scale q_i.k_j)) v_j over the keys j with 0 <= i - j < window (window <= 0: all
 //                                  j <= i), cap(s) = c tanh(s / c), c = softcap (softcap <= 0: none); query head h reads key/value
-//                                  head h / (H / G); the key range is cut into splits for few tokens on long ranges
+//                                  head h / (H / G); the key range is cut into splits for few tokens on long ranges; bf16 with head
+//                                  sizes that are multiples of 16 up to 128: m16n8k16 tensor-core tiles
 //
 // Storage type T (bf16 or float) for activations and cache rows; rotation, norms, scores, the cap and the soft-max are fp32
 // (angles fp64).  Cache row of a token: [k G*d | v G*dv]; a sequence's page table row is a ring.
@@ -14,6 +15,7 @@
 
 #include "common.cuh"
 #include "seq_common.cuh"
+#include "mma_tile.cuh"
 
 namespace ktb {
 
@@ -161,6 +163,227 @@ __global__ void __launch_bounds__(256) window_softmax_attn_kernel(const T* __res
     }
 }
 
+// ------------------------------------------------------------------------------------------------ soft-max attention, tensor cores (bf16)
+// A CTA of ROWS / 16 warps owns a tile of ROWS rows = (token, query head) pairs of ONE sequence portion and ONE key/value head: `RH`
+// query heads of the group for each of ROWS / RH consecutive tokens (prompt portions fill the rows with tokens, decode steps with the
+// group's heads, so grouped heads share every key tile).  Keys run in tiles of KEYS through a two-stage cp.async ring of [k | v]
+// rows gathered through the page table, from the first key that the tile's earliest token still sees to its last token's own;
+// S = Q K^T and O += P V are m16n8k16 bf16 MMAs with fp32 accumulators; scale, cap, window and causal masks, running maximum and
+// sum in fp32 registers (a row's maximum over the four threads that hold it); the weights go to the second product as bf16.
+// grid (tile bound, G * head blocks, splits); tiles are found from the per-sequence rows `seqs`.
+constexpr int kMmaRows = 64, kMmaKeys = 32, kMmaPad = 8;
+__device__ __forceinline__ float cap_score_fast(float s, float two_over_cap, float softcap) {
+    // c tanh(s / c) as c (1 - 2 / (exp(2 s / c) + 1)), c = softcap: absolute error of a few 1e-7 of the cap
+    return softcap * (1.0f - __fdividef(2.0f, __expf(s * two_over_cap) + 1.0f));
+}
+
+template <int D16MAX, int DV16MAX>
+__global__ void __launch_bounds__(kMmaRows * 2, D16MAX <= 4 ? 4 : 3) window_softmax_attn_mma_kernel(
+    const __nv_bfloat16* __restrict__ q, int H, int G, int d, int dv, float scale, float softcap, int window, const int* __restrict__ pos, const int* __restrict__ slot,
+    const int* __restrict__ seqs, int seqs_stride, int n_seqs, int RH, const int* __restrict__ page_table, int max_pages, int page_size, const __nv_bfloat16* __restrict__ cache,
+    __nv_bfloat16* __restrict__ out, float* __restrict__ partial) {
+    constexpr int ROWS = kMmaRows, KEYS = kMmaKeys;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int tile_info[3];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
+    const int TOKS = ROWS / RH;
+    if (tid == 0) {      // which sequence portion and which of its tokens this tile covers
+        int b = blockIdx.x, found = -1, off = 0, len = 0;
+        for (int s = 0; s < n_seqs; s++) {
+            len = seqs[seqs_stride + s];
+            const int nt = (len + TOKS - 1) / TOKS;
+            if (b < nt) { found = s; off = b * TOKS; break; }
+            b -= nt;
+        }
+        tile_info[0] = found;
+        tile_info[1] = found >= 0 ? seqs[found] + off : 0;
+        tile_info[2] = found >= 0 ? min(TOKS, len - off) : 0;
+    }
+    __syncthreads();
+    if (tile_info[0] < 0) return;
+    const int tok0 = tile_info[1], ntok = tile_info[2];
+    const int R = H / G, hblocks = R / RH;
+    const int g = blockIdx.y / hblocks, h0 = g * R + (blockIdx.y % hblocks) * RH;
+    const int d16 = d >> 4, dv16 = dv >> 4, ldk = d + kMmaPad, ldv = dv + kMmaPad;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* Ks = Qs + ROWS * ldk;                     // [2][KEYS][ldk]
+    __nv_bfloat16* Vs = Ks + 2 * KEYS * ldk;                 // [2][KEYS][ldv]
+    const int pos0 = pos[tok0], max_pos = pos0 + ntok - 1;
+    // the tile's key range [lo, max_pos], cut into this split's part in whole key tiles counted from lo
+    const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int splits = gridDim.z, n_keys = max_pos + 1 - lo;
+    const int per = ((n_keys + splits - 1) / splits + KEYS - 1) / KEYS * KEYS;
+    const int k_lo = lo + blockIdx.z * per, k_hi = min(max_pos + 1, k_lo + per);
+    // this thread's two rows of the warp's 16
+    const int rA = warp * 16 + gq, rB = rA + 8;
+    const int tokA = rA / RH, tokB = rB / RH, hA = h0 + rA % RH, hB = h0 + rB % RH;
+    const bool vA = tokA < ntok, vB = tokB < ntok;
+    const int pA = pos0 + tokA, pB = pos0 + tokB;
+    const bool warp_live = (warp * 16) / RH < ntok;
+    const int warp_max_pos = pos0 + min(ntok - 1, (warp * 16 + 15) / RH), warp_min_pos = pos0 + (warp * 16) / RH;
+    const int warp_first_key = window > 0 ? warp_min_pos - window + 1 : 0;      // no row of this warp sees a key before this one
+    const float two_over_cap = softcap > 0.f ? 2.0f / softcap : 0.f;
+    float O[2 * DV16MAX][4];
+#pragma unroll
+    for (int n = 0; n < 2 * DV16MAX; n++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) O[n][e] = 0.f;
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+    if (k_lo < k_hi) {
+        const int* pt = page_table + (long)slot[tok0] * max_pages;
+        const long cw = (long)G * (d + dv);
+        const int kc = d >> 3, vc = dv >> 3;      // 16-byte chunks per row
+        for (int i = tid; i < ROWS * kc; i += blockDim.x) {
+            const int r = i / kc, c = i - r * kc, tk = r / RH;
+            const bool ok = tk < ntok;
+            cp_async16(Qs + r * ldk + c * 8, ok ? q + ((long)(tok0 + tk) * H + h0 + r % RH) * d + c * 8 : q, ok);
+        }
+        // TPR neighbouring threads copy key row r of a tile: one page-table lookup per thread and tile, made a tile ahead of its copies
+        constexpr int TPR = ROWS * 2 / KEYS;
+        const int lrow = tid / TPR, lpar = tid % TPR;
+        auto row_base = [&](int kp) -> long {
+            return kp < k_hi ? ((long)pt[(kp / page_size) % max_pages] * page_size + kp % page_size) * cw : -1;
+        };
+        auto load_tile = [&](int stage, long base) {
+            __nv_bfloat16* kd = Ks + stage * KEYS * ldk + lrow * ldk;
+            __nv_bfloat16* vd = Vs + stage * KEYS * ldv + lrow * ldv;
+            const bool ok = base >= 0;
+            const __nv_bfloat16* ksrc = ok ? cache + base + (long)g * d : cache;
+            const __nv_bfloat16* vsrc = ok ? cache + base + (long)G * d + (long)g * dv : cache;
+            for (int c = lpar; c < kc; c += TPR) cp_async16(kd + c * 8, ok ? ksrc + c * 8 : cache, ok);
+            for (int c = lpar; c < vc; c += TPR) cp_async16(vd + c * 8, ok ? vsrc + c * 8 : cache, ok);
+        };
+        load_tile(0, row_base(k_lo + lrow));
+        long next_base = row_base(k_lo + KEYS + lrow);
+        int stage = 0;
+        for (int j0 = k_lo; j0 < k_hi; j0 += KEYS, stage ^= 1) {
+            cp_async_wait_all();
+            __syncthreads();      // this tile has landed, and every warp is done with the other stage
+            if (j0 + KEYS < k_hi) {
+                load_tile(stage ^ 1, next_base);
+                next_base = row_base(j0 + 2 * KEYS + lrow);
+            }
+            if (!warp_live || j0 > warp_max_pos || j0 + KEYS <= warp_first_key) continue;
+            const __nv_bfloat16* kt = Ks + stage * KEYS * ldk;
+            const __nv_bfloat16* vt = Vs + stage * KEYS * ldv;
+            float S[KEYS / 8][4];
+#pragma unroll
+            for (int n = 0; n < KEYS / 8; n++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) S[n][e] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < D16MAX; kk++) {
+                if (kk < d16) {
+                    uint32_t a[4];
+                    ldmatrix_x4(a, Qs + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ldk + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+                    for (int np = 0; np < KEYS / 16; np++) {      // two key n-tiles per ldmatrix
+                        uint32_t b[4];
+                        ldmatrix_x4(b, kt + (np * 16 + (lane & 7) + 8 * (lane >> 4)) * ldk + kk * 16 + 8 * ((lane >> 3) & 1));
+                        mma_bf16_16816(S[2 * np], a, b[0], b[1]);
+                        mma_bf16_16816(S[2 * np + 1], a, b[2], b[3]);
+                    }
+                }
+            }
+            // nothing to mask: all 16 rows carry tokens, and every key of the tile lies at or before the earliest of them, inside the
+            // window of the latest and inside this split
+            const bool plain = (warp * 16 + 15) / RH < ntok && j0 + KEYS - 1 <= warp_min_pos && (window <= 0 || j0 > warp_max_pos - window) && j0 + KEYS <= k_hi;
+            float tmA = -INFINITY, tmB = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < KEYS / 8; n++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    float s = S[n][e] * scale;
+                    if (softcap > 0.f) s = cap_score_fast(s, two_over_cap, softcap);
+                    if (!plain) {
+                        const int key = j0 + n * 8 + 2 * tq + (e & 1);
+                        const bool second = e >= 2;
+                        const int dist = (second ? pB : pA) - key;
+                        const bool ok = (second ? vB : vA) && dist >= 0 && (window <= 0 || dist < window) && key < k_hi;
+                        if (!ok) s = -INFINITY;
+                    }
+                    S[n][e] = s;
+                    if (e < 2) tmA = fmaxf(tmA, s);
+                    else tmB = fmaxf(tmB, s);
+                }
+            }
+            tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 1));
+            tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 2));
+            tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 1));
+            tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 2));
+            const float nA = fmaxf(mA, tmA), nB = fmaxf(mB, tmB);
+            const float uA = nA == -INFINITY ? 0.f : nA, uB = nB == -INFINITY ? 0.f : nB;      // a row that has seen no key yet keeps weights of zero
+            const float cA = __expf(mA - uA), cB = __expf(mB - uB);
+            mA = nA;
+            mB = nB;
+            float sA = 0.f, sB = 0.f;
+#pragma unroll
+            for (int n = 0; n < KEYS / 8; n++) {
+                S[n][0] = __expf(S[n][0] - uA);
+                S[n][1] = __expf(S[n][1] - uA);
+                S[n][2] = __expf(S[n][2] - uB);
+                S[n][3] = __expf(S[n][3] - uB);
+                sA += S[n][0] + S[n][1];
+                sB += S[n][2] + S[n][3];
+            }
+            lA = lA * cA + sA;
+            lB = lB * cB + sB;
+#pragma unroll
+            for (int n = 0; n < 2 * DV16MAX; n++) {
+                O[n][0] *= cA;
+                O[n][1] *= cA;
+                O[n][2] *= cB;
+                O[n][3] *= cB;
+            }
+#pragma unroll
+            for (int kk = 0; kk < KEYS / 16; kk++) {      // 16 keys per step
+                uint32_t a[4] = {pack_bf16(S[2 * kk][0], S[2 * kk][1]), pack_bf16(S[2 * kk][2], S[2 * kk][3]), pack_bf16(S[2 * kk + 1][0], S[2 * kk + 1][1]),
+                                 pack_bf16(S[2 * kk + 1][2], S[2 * kk + 1][3])};
+#pragma unroll
+                for (int vp = 0; vp < DV16MAX; vp++) {
+                    if (vp < dv16) {
+                        uint32_t b[4];
+                        ldmatrix_x4_trans(b, vt + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ldv + vp * 16 + 8 * (lane >> 4));
+                        mma_bf16_16816(O[2 * vp], a, b[0], b[1]);
+                        mma_bf16_16816(O[2 * vp + 1], a, b[2], b[3]);
+                    }
+                }
+            }
+        }
+        cp_async_wait_all();
+    }
+    lA += __shfl_xor_sync(0xffffffffu, lA, 1);
+    lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 1);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    if (partial) {      // [T][H][splits][dv + 2]: running maximum, sum, un-normalised weighted values
+        float* oA = partial + (((long)(tok0 + tokA) * H + hA) * splits + blockIdx.z) * (dv + 2);
+        float* oB = partial + (((long)(tok0 + tokB) * H + hB) * splits + blockIdx.z) * (dv + 2);
+        if (tq == 0) {
+            if (vA) { oA[0] = mA; oA[1] = lA; }
+            if (vB) { oB[0] = mB; oB[1] = lB; }
+        }
+#pragma unroll
+        for (int n = 0; n < 2 * DV16MAX; n++) {
+            const int col = n * 8 + 2 * tq;
+            if (col < dv) {
+                if (vA) *reinterpret_cast<float2*>(oA + 2 + col) = make_float2(O[n][0], O[n][1]);
+                if (vB) *reinterpret_cast<float2*>(oB + 2 + col) = make_float2(O[n][2], O[n][3]);
+            }
+        }
+    } else {
+        const float iA = vA ? 1.0f / lA : 0.f, iB = vB ? 1.0f / lB : 0.f;
+#pragma unroll
+        for (int n = 0; n < 2 * DV16MAX; n++) {
+            const int col = n * 8 + 2 * tq;
+            if (col < dv) {
+                if (vA) *reinterpret_cast<uint32_t*>(out + ((long)(tok0 + tokA) * H + hA) * dv + col) = pack_bf16(O[n][0] * iA, O[n][1] * iA);
+                if (vB) *reinterpret_cast<uint32_t*>(out + ((long)(tok0 + tokB) * H + hB) * dv + col) = pack_bf16(O[n][2] * iB, O[n][3] * iB);
+            }
+        }
+    }
+}
+
 // one warp per (token, head): the parts' weights exp(m_s - m) / l (parts without a key have m = -inf and weigh nothing), then
 // the columns in parallel, parts in order
 template <typename T>
@@ -226,15 +449,48 @@ extern "C" size_t ktb200_window_softmax_attn_workspace(int n_tokens, int heads, 
     return splits > 1 ? (size_t)n_tokens * heads * splits * (vdim + 2) * sizeof(float) : 0;
 }
 
+/* whether ktb200_window_softmax_attn runs tensor-core tiles for these sizes (bf16, head sizes multiples of 16 up to 128, and
+ * `seqs` given), and an upper bound of its row tiles per key/value head (for choosing splits) */
+extern "C" int ktb200_window_softmax_attn_uses_tensor_cores(int heads, int kv_heads, int dim, int vdim, int dtype) {
+    return dtype == KTB200_TYPE_BF16 && kv_heads > 0 && heads % kv_heads == 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 128 && vdim <= 128;
+}
+extern "C" int ktb200_window_softmax_attn_tiles(int heads, int kv_heads, int n_tokens, int n_seqs) {
+    return n_seqs + n_tokens / (kMmaRows / mma_heads_per_tile(heads / kv_heads));
+}
+
 extern "C" int ktb200_window_softmax_attn(const void* q, int heads, int kv_heads, int dim, int vdim, float scale, float softcap, int window, const int* pos, const int* slot,
-                                          const int* page_table, int max_pages, int page_size, const void* cache, void* out, int n_tokens, int splits, float* workspace,
-                                          int dtype, void* stream) {
+                                          const int* seqs, int seqs_stride, int n_seqs, const int* page_table, int max_pages, int page_size, const void* cache, void* out,
+                                          int n_tokens, int splits, float* workspace, int dtype, int allow_tensor_cores, void* stream) {
     if (!q || !pos || !slot || !page_table || !cache || !out || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0 || vdim > 32 * kSmMaxCols ||
         splits < 1 || (splits > 1 && !workspace) || page_size <= 0 || max_pages <= 0) {
         set_error("window_softmax_attn: bad argument (value size <= %d)", 32 * kSmMaxCols);
         return KTB200_EINVAL;
     }
     if (n_tokens <= 0) return KTB200_OK;
+    const long rows = (long)n_tokens * heads;
+    const long merge_blocks = (rows + 7) / 8;
+    if (allow_tensor_cores && seqs && n_seqs > 0 && ktb200_window_softmax_attn_uses_tensor_cores(heads, kv_heads, dim, vdim, dtype)) {
+        using B = __nv_bfloat16;
+        const int RH = mma_heads_per_tile(heads / kv_heads);
+        const dim3 grid(ktb200_window_softmax_attn_tiles(heads, kv_heads, n_tokens, n_seqs), kv_heads * (heads / kv_heads / RH), splits);
+        const size_t smem = (((size_t)kMmaRows + 2 * kMmaKeys) * (dim + kMmaPad) + (size_t)2 * kMmaKeys * (vdim + kMmaPad)) * sizeof(B);
+#define MMA_LAUNCH(DK, DV)                                                                                                                                      \
+    do {                                                                                                                                                        \
+        GRANT_SMEM((window_softmax_attn_mma_kernel<DK, DV>), smem);                                                                                             \
+        window_softmax_attn_mma_kernel<DK, DV><<<grid, kMmaRows * 2, smem, (cudaStream_t)stream>>>((const B*)q, heads, kv_heads, dim, vdim, scale, softcap, window, pos, slot, \
+                                                                                                   seqs, seqs_stride, n_seqs, RH, page_table, max_pages, page_size,  \
+                                                                                                   (const B*)cache, (B*)out, splits > 1 ? workspace : nullptr);   \
+    } while (0)
+        if (dim <= 64 && vdim <= 64) MMA_LAUNCH(4, 4);
+        else MMA_LAUNCH(8, 8);
+#undef MMA_LAUNCH
+        KTB_LAUNCH_CHECK();
+        if (splits > 1) {
+            softmax_merge_kernel<B><<<(int)(merge_blocks < 148 * 8 ? merge_blocks : 148 * 8), 256, 0, (cudaStream_t)stream>>>(workspace, splits, (B*)out, rows, vdim);
+            KTB_LAUNCH_CHECK();
+        }
+        return KTB200_OK;
+    }
     const int R = heads / kv_heads, HB = R < 8 ? R : 8, hblocks = (R + HB - 1) / HB;
     const size_t smem = ((size_t)HB * dim + (size_t)kSmTile * (dim + 1) + (size_t)kSmTile * vdim + (size_t)HB * kSmTile) * sizeof(float);
     if (smem > 200 * 1024) { set_error("window_softmax_attn: head too wide for shared memory"); return KTB200_EINVAL; }
@@ -245,9 +501,7 @@ extern "C" int ktb200_window_softmax_attn(const void* q, int heads, int kv_heads
             splits > 1 ? workspace : nullptr, n_tokens);
         KTB_LAUNCH_CHECK();
         if (splits > 1) {
-            const long rows = (long)n_tokens * heads;
-            const long blocks = (rows + 7) / 8;
-            softmax_merge_kernel<T><<<(int)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, (cudaStream_t)stream>>>(workspace, splits, (T*)out, rows, vdim);
+            softmax_merge_kernel<T><<<(int)(merge_blocks < 148 * 8 ? merge_blocks : 148 * 8), 256, 0, (cudaStream_t)stream>>>(workspace, splits, (T*)out, rows, vdim);
             KTB_LAUNCH_CHECK();
         }
     });

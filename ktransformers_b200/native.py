@@ -134,7 +134,9 @@ SEQ_SYMBOLS = {
     # csrc/softmax_attn.cu, csrc/delta_rule.cu
     "ktb200_rope_norm_cache_write": (_I, [_VP, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _VP, _I, _F, _VP, _L, _VP, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP]),
     "ktb200_window_softmax_attn_workspace": (C.c_size_t, [_I, _I, _I, _I]),
-    "ktb200_window_softmax_attn": (_I, [_VP, _I, _I, _I, _I, _F, _F, _I, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP, _I, _VP]),
+    "ktb200_window_softmax_attn": (_I, [_VP, _I, _I, _I, _I, _F, _F, _I, _VP, _VP, _VP, _I, _I, _VP, _I, _I, _VP, _VP, _I, _I, _VP, _I, _I, _VP]),
+    "ktb200_window_softmax_attn_uses_tensor_cores": (_I, [_I, _I, _I, _I, _I]),
+    "ktb200_window_softmax_attn_tiles": (_I, [_I, _I, _I, _I]),
     "ktb200_delta_prep": (_I, [_VP, _L, _I, _I, _I, _VP, _I, _VP, _VP, _I, _I, _I, _I, _F, _VP, _VP, _I, _VP, _L, _VP, _VP, _VP, _VP, _VP, _I, _I, _VP]),
     "ktb200_delta_scan": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP, _I, _I, _VP, _L, _VP, _VP]),
 }

@@ -319,6 +319,10 @@ class KCappedWindowAttention(torch.nn.Module):
         o_i     = sum_j softmax_j(s_ij) v_j                     ktb200_window_softmax_attn (fp32 scores and weights)
         out     = W_o o                                         GEMM
 
+    Two attention kernels (csrc/softmax_attn.cu): in bf16 with head sizes that are multiples of 16 up to 128, tiles of 64 (token,
+    head) rows against 32 keys on the tensor cores (the weights leave the fp32 soft-max as bf16 operands of the second product);
+    any other size, and fp32, on CUDA cores with fp32 products throughout.
+
     The blended v is what is cached.  `forward` also returns the layer's own values before the blend (a view of P), which the
     model hands to later layers as their `v_other`.  Sizes, scale, cap, window, the rotation's constants and layout and the
     unit-rms switch are constructor parameters (models/configuration_zivulix.CappedWindowAttentionSpec); `cache_idx` picks
@@ -347,13 +351,20 @@ class KCappedWindowAttention(torch.nn.Module):
             self.vmix.data.copy_(t("vmix").float().reshape(1))
         self.o.data.copy_(t("o"))
 
-    def pick_splits(self, n_tokens: int, max_kv: int) -> int:
+    use_tensor_cores = True
+
+    def pick_splits(self, n_tokens: int, max_kv: int, n_seqs: int = 0, tensor_cores: bool = False) -> int:
         """Cut the key range when a small batch would leave most SMs idle on a long range."""
         s = self.spec
         keys = min(s.window, max_kv) if s.window else max_kv
-        ctas = n_tokens * s.kv_heads * ((s.heads // s.kv_heads + 7) // 8)
+        if tensor_cores:
+            ctas = native.seq_lib().ktb200_window_softmax_attn_tiles(s.heads, s.kv_heads, n_tokens, n_seqs) * s.kv_heads
+        else:
+            ctas = n_tokens * s.kv_heads * ((s.heads // s.kv_heads + 7) // 8)
         if ctas >= 148 or keys <= 256:
             return 1
+        if tensor_cores:      # four CTAs per SM; parts of 64 keys or more
+            return max(1, min(128, keys // 64, 1184 // ctas))
         return max(1, min(64, keys // 128, 592 // ctas))
 
     def forward(self, h: torch.Tensor, batch, cache, cache_idx: int, v_other: Optional[torch.Tensor] = None):
@@ -372,9 +383,11 @@ class KCappedWindowAttention(torch.nn.Module):
                                                           self.vmix.data_ptr(), batch.pos.data_ptr(), batch.slot.data_ptr(), cache.page_table.data_ptr(),
                                                           cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), q.data_ptr(), T, code, st))
         o = torch.empty((T, s.heads * s.vdim), dtype=dt, device=dev)
-        splits = self.pick_splits(T, batch.max_kv)
+        tc = bool(self.use_tensor_cores and batch.seqs is not None and lib.ktb200_window_softmax_attn_uses_tensor_cores(s.heads, s.kv_heads, s.dim, s.vdim, code))
+        splits = self.pick_splits(T, batch.max_kv, batch.n_seqs, tc)
         ws = torch.empty(lib.ktb200_window_softmax_attn_workspace(T, s.heads, s.vdim, splits) // 4, dtype=torch.float32, device=dev) if splits > 1 else None
         native.check_seq(lib.ktb200_window_softmax_attn(q.data_ptr(), s.heads, s.kv_heads, s.dim, s.vdim, float(s.scale), float(s.softcap or 0.0), int(s.window or 0),
-                                                        batch.pos.data_ptr(), batch.slot.data_ptr(), cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size,
-                                                        kv.data_ptr(), o.data_ptr(), T, splits, ws.data_ptr() if ws is not None else None, code, st))
+                                                        batch.pos.data_ptr(), batch.slot.data_ptr(), batch.seqs.data_ptr() if tc else None, batch.seqs.stride(0) if tc else 0,
+                                                        batch.n_seqs if tc else 0, cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size, kv.data_ptr(),
+                                                        o.data_ptr(), T, splits, ws.data_ptr() if ws is not None else None, code, int(tc), st))
         return torch.nn.functional.linear(o, self.o), v_own

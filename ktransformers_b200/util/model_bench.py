@@ -189,7 +189,7 @@ def kernel_leg(flush, peak_gbs, have_main_lib):
         sink = torch.zeros(NH, device=dev)
         splits = max(1, min(32, ctx // 128, 296 // (B * NH // 8)))
         ws = torch.empty(max(1, seq.ktb200_latent_window_attn_workspace(B, NH, R, splits) // 4), device=dev)
-        fn = lambda: native.check_seq(seq.ktb200_latent_window_attn(q.data_ptr(), q_abs.data_ptr(), NH, NOPE, ROPE, R, ROPE, inv.data_ptr(), 0.07, sink.data_ptr(), ctx, pos.data_ptr(),
+        fn = lambda: native.check_seq(seq.ktb200_latent_window_attn(q.data_ptr(), q_abs.data_ptr(), NH, NOPE, ROPE, R, ROPE, 0, inv.data_ptr(), 0.07, sink.data_ptr(), ctx, pos.data_ptr(),
                                                                     slot.data_ptr(), ptab.data_ptr(), pages, PAGE, cache.data_ptr(), lat.data_ptr(), B, splits, ws.data_ptr(), 30, S()))
         ours = timed(fn, flush)
         nbytes = B * ctx * (R + ROPE) * 2
@@ -226,7 +226,7 @@ def kernel_leg(flush, peak_gbs, have_main_lib):
     tws = torch.empty(wsb // 4, device=dev)
     f_tc = lambda: native.check_seq(seq.ktb200_latent_window_attn_tc(q_abs.data_ptr(), q_rot.data_ptr(), NH, 0.07, sink.data_ptr(), ctx, pos.data_ptr(), slot.data_ptr(), ptab.data_ptr(),
                                                                      pages, PAGE, cache.data_ptr(), (pages + 1) * PAGE, lat.data_ptr(), T, ctx, tws.data_ptr(), wsb, S()))
-    f_cc = lambda: native.check_seq(seq.ktb200_latent_window_attn(q.data_ptr(), q_abs.data_ptr(), NH, NOPE, ROPE, R, ROPE, inv.data_ptr(), 0.07, sink.data_ptr(), ctx, pos.data_ptr(),
+    f_cc = lambda: native.check_seq(seq.ktb200_latent_window_attn(q.data_ptr(), q_abs.data_ptr(), NH, NOPE, ROPE, R, ROPE, 0, inv.data_ptr(), 0.07, sink.data_ptr(), ctx, pos.data_ptr(),
                                                                   slot.data_ptr(), ptab.data_ptr(), pages, PAGE, cache.data_ptr(), lat.data_ptr(), T, 1, None, 30, S()))
     for name, f, it in (("mla_decode_tc_kernel<split P> (+merge with sink)", f_tc, 5), ("latent_window_attn_kernel", f_cc, 2)):
         ms = timed(f, flush, iters=it, warmup=1)
@@ -286,7 +286,7 @@ def mabidra_kernel_leg(flush, peak_gbs, peak_tflops):
         x, y, w1, w2 = rn(T, D, dt=torch.float32), rn(T, D), rn(D), rn(D)
         xo, h = torch.empty_like(x), torch.empty(T, D, dtype=bf, device=dev)
         ours = timed(lambda: native.check_seq(seq.ktb200_group_rmsnorm_sandwich(x.data_ptr(), y.data_ptr(), 30, w1.data_ptr(), None, xo.data_ptr(), w2.data_ptr(), h.data_ptr(), 4,
-                                                                                1e-5, T, D, 30, S())), flush)
+                                                                                1e-5, 0.0, T, D, 30, S())), flush)
         a, b, mu, hs = rn(T, D), rn(T, D), rn(D), torch.empty(T, D, dtype=bf, device=dev)
         meta = torch.tensor([[-1] + list(range(T - 1)), [-1] * T, [-1] * (T - 1) + [0]], dtype=torch.int32, device=dev)
         st = torch.zeros(2, D, device=dev)

@@ -219,6 +219,7 @@ def mixer_alone(desc, dtype, n, page_size, portions, big_at=None, big=30.0, seed
     spec = MIXER_SPECS[desc["type"]](m)
     if desc["type"] == "attention":
         op = KCappedWindowAttention(width, spec, 1e-5, dtype=dtype)
+        op.use_tensor_cores = tensor_path
     elif desc["type"] == "latent_attention":
         op = KLatentWindowAttention(width, spec, 1e-5, 0, dtype=dtype)
         op.use_tensor_path = tensor_path
@@ -322,6 +323,53 @@ def test_far_value_among_hundreds_and_the_split_path():
     assert rel(got, want) < 4e-2
 
 
+MMA_SHAPES = [U.attn(heads=8, kv_heads=2, dim=16, vdim=32, window=40, rot_dims=16), U.attn(heads=9, kv_heads=1, dim=48, vdim=16, window=None, softcap=None, rot_dims=32),
+              U.attn(heads=34, kv_heads=2, dim=32, vdim=32, window=33), U.attn(heads=4, kv_heads=4, dim=128, vdim=128, window=100, rot_dims=64, softcap=30.0),
+              U.attn(heads=12, kv_heads=1, dim=64, vdim=80, window=64, factor=None), U.attn(heads=40, kv_heads=2, dim=16, vdim=112, window=7, softcap=0.8)]
+
+
+@gpu
+@pytest.mark.parametrize("desc", MMA_SHAPES)
+def test_tensor_core_attention_path(desc):
+    """bf16 with head sizes that are multiples of 16 takes the tensor-core tiles: against the restatement, and against the
+    CUDA-core kernel on the same bf16 inputs (between the two: bf16 weights in the second product, and the order of the sums).
+    200 tokens cross several key tiles; portions start and end inside tiles; the value that stands out sits at a tile's edge"""
+    for portions, at in (([200], 7), ([129, 1, 1, 30, 2, 37], 63), ([64, 64, 8, 1], 64), ([190] + [1] * 10, 127)):
+        got, want = mixer_alone(desc, torch.bfloat16, 200, 16, portions, big_at=at, big=4.0)
+        simple, _ = mixer_alone(desc, torch.bfloat16, 200, 16, portions, big_at=at, big=4.0, tensor_path=False)
+        assert rel(got, want) < 4e-2 and rel(simple, want) < 4e-2
+        assert rel(got, simple) < 1.5e-2
+        assert rel(got[:3], want[:3]) < 4e-2 and rel(got[at:at + 3], want[at:at + 3]) < 4e-2
+
+
+@gpu
+@pytest.mark.parametrize("window", [1, 2, 31, 32, 33, 64, 65, 100])
+@pytest.mark.parametrize("decode", [False, True])
+def test_tensor_core_window_edges_inside_and_between_key_tiles(window, decode):
+    """the value of token 40 stands out: the last row that sees it and the first that does not, for windows that end inside,
+    on and just behind a 32-key tile; a window one longer must differ at that row"""
+    mk = lambda w: U.attn(heads=8, kv_heads=2, dim=32, vdim=32, window=w, softcap=None, rot_dims=16)
+    n = 40 + window + 12
+    portions = [41] + [1] * n if decode else [37, 2, n]
+    got, want = mixer_alone(mk(window), torch.bfloat16, n, 16, portions, big_at=40, big=6.0)
+    assert rel(got, want) < 4e-2
+    for r in (40, 40 + window - 1, 40 + window, 40 + window + 1):
+        assert rel(got[r], want[r]) < 4e-2
+    _, shifted = mixer_alone(mk(window + 1), torch.bfloat16, n, 16, [n], big_at=40, big=6.0)
+    assert rel(shifted[40 + window], want[40 + window]) > 0.08      # the test bites: twice the tolerance even with a hundred keys in sight
+
+
+@gpu
+def test_tensor_core_attention_far_value_and_split_edges():
+    """decode over a long range on the tensor-core path cuts the keys into parts of whole tiles"""
+    for window in (None, 600):
+        desc = U.attn(heads=16, kv_heads=2, dim=32, vdim=48, window=window)
+        for at in (3, 127, 128, 383, 384, 640):
+            got, want = mixer_alone(desc, torch.bfloat16, 700, 64, [690] + [1] * 10, big_at=at, big=4.0)
+            simple, _ = mixer_alone(desc, torch.bfloat16, 700, 64, [690] + [1] * 10, big_at=at, big=4.0, tensor_path=False)
+            assert rel(got, want) < 4e-2 and rel(got[690:], want[690:]) < 4e-2 and rel(got, simple) < 1.5e-2
+
+
 LATENT_SHAPES = [U.latent(), U.latent(heads=1, dim=3, rot_dim=2, vdim=7, kv_rank=33), U.latent(heads=9, dim=16, rot_dim=16, vdim=8, kv_rank=40, base=5e5), U.latent(heads=16, dim=8, rot_dim=6, vdim=20, kv_rank=130)]
 
 
@@ -411,6 +459,20 @@ def test_prompt_decode_and_portions_agree_with_the_restatement(tmp_path, dtype, 
         got = run_steps(eng, cut("p", t, sizes))["p"]
         assert err(got, want) < tol
         assert err(got, whole) < (2e-5 if dtype == "float32" else tol)   # the cut does not matter beyond rounding
+
+
+@gpu
+def test_whole_model_in_bf16_on_tensor_core_head_sizes(tmp_path):
+    """head sizes that are multiples of 16: bf16 attention runs on the tensor-core tiles inside a whole model (grouped heads,
+    blended values, 150 tokens over several key tiles), whole, in portions and with a decoded tail"""
+    layers = [(U.attn(heads=6, kv_heads=2, dim=32, vdim=48, window=40, rot_dims=16, v_mix=True), U.dense(96)), (U.delta(heads=4, kv_heads=2, dim=32, vdim=16), None),
+              (U.attn(heads=4, kv_heads=2, dim=16, vdim=48, window=None, v_mix=True), U.dense(64)), (U.latent(heads=4, dim=16, rot_dim=16, vdim=16, kv_rank=32), None)]
+    cfg = U.config(layers, width=64, vocab=90)
+    eng, om = serve(tmp_path, cfg, "bfloat16", seed=3, max_tokens=512, max_slots=2, page_size=16)
+    t = toks(150, 90, seed=9)
+    want = oracle_logits(om, t)
+    for k, sizes in enumerate(([150], [70, 3, 2, 40, 1, 34], [130] + [1] * 20)):
+        assert rel_rows(run_steps(eng, cut(("m", k), t, sizes))[("m", k)], want) < BF16_TOL
 
 
 @gpu
