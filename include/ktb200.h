@@ -458,7 +458,7 @@ int ktb200_gated_act_mul(const void* gate_up, void* out, int n_tokens, int ff, i
  *                                  SiLU; q, k -> x * rsqrt(|x|^2 + unit_eps) per head, q also / sqrt(dim); beta = sigmoid(proj[b_off + h]),
  *                                  decay = exp(-rate softplus(proj[a_off + h] + dt_bias[h])), rate = exp(a_log[h]); seq_of[t]: the portion of token t
  *   ktb200_delta_scan              per portion seqs[0..3][s] and head: M <- a M; r = eta (v - M^T k); M <- M + k r^T; y = M^T q.
- *                                  State rows: [M heads*dim*vdim | conv inputs (taps - 1)*channels] fp32, row stride state_stride; dim <= 256 */
+ *                                  State rows: [M heads*dim*vdim | conv inputs (taps - 1)*channels] fp32, row stride state_stride; dim, vdim <= 256 */
 int ktb200_rope_norm_cache_write(const void* proj, long proj_stride, int q_off, int k_off, int v_off, int heads, int kv_heads, int dim, int vdim,
                                  int rot_dims, int rot_layout, const double* inv_freq, int unit_rms, float eps, const void* v_other, long v_other_stride,
                                  const float* blend, const int* pos, const int* slot, const int* page_table, int max_pages, int page_size, void* cache,

@@ -22,52 +22,64 @@ __device__ __forceinline__ float dr_sigmoid(float x) { return __fdiv_rn(1.0f, 1.
 __device__ __forceinline__ float dr_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 // ------------------------------------------------------------------------------------------------ convolution, activations, unit vectors, gates
-// One CTA per token.  Channels c < C = 2 G d + H dv are the columns qkv_off + c of proj: [q G*d | k G*d | v H*dv].  Shared memory: y[C].
+// grid (tokens, blocks of kPrepUnits units); a unit is one head's run of channels: 2 G query / key heads of d channels, then H value
+// heads of dv channels, in the order of the columns qkv_off .. of proj: [q G*d | k G*d | v H*dv].  A warp per unit, a lane keeps up to
+// kPrepPerLane channels in registers.  The CTAs of a portion's last token also move the last taps - 1 inputs into the state row; the
+// first block of every token computes the step sizes and decays.
+constexpr int kPrepUnits = 8;
+constexpr int kPrepPerLane = 8;      // head size <= 256
 template <typename T>
-__global__ void __launch_bounds__(256) delta_prep_kernel(const T* __restrict__ proj, long proj_stride, int qkv_off, int b_off, int a_off, const T* __restrict__ conv_w, int taps,
-                                                         const float* __restrict__ a_log, const float* __restrict__ dt_bias, int H, int G, int d, int dv, float unit_eps,
-                                                         const int* __restrict__ seq_of, const int* __restrict__ seqs, int seqs_stride, float* __restrict__ state,
-                                                         long state_stride, long conv_off, float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vv,
-                                                         float* __restrict__ beta, float* __restrict__ decay) {
-    extern __shared__ __align__(16) float ys[];
+__global__ void __launch_bounds__(kPrepUnits * 32) delta_prep_kernel(const T* __restrict__ proj, long proj_stride, int qkv_off, int b_off, int a_off, const T* __restrict__ conv_w,
+                                                                     int taps, const float* __restrict__ a_log, const float* __restrict__ dt_bias, int H, int G, int d, int dv,
+                                                                     float unit_eps, const int* __restrict__ seq_of, const int* __restrict__ seqs, int seqs_stride,
+                                                                     float* __restrict__ state, long state_stride, long conv_off, float* __restrict__ qn, float* __restrict__ kn,
+                                                                     float* __restrict__ vv, float* __restrict__ beta, float* __restrict__ decay) {
     const long t = blockIdx.x;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int s = seq_of[t];
     const int start = seqs[s], len = seqs[seqs_stride + s], rd = seqs[2 * seqs_stride + s], wr = seqs[3 * seqs_stride + s];
     const int off = (int)t - start, C = 2 * G * d + H * dv, back = taps - 1;
+    if (blockIdx.y == 0) {
+        for (int h = tid; h < H; h += blockDim.x) {
+            beta[t * H + h] = dr_sigmoid(to_f(proj[t * proj_stride + b_off + h]));
+            decay[t * H + h] = expf(-expf(a_log[h]) * dr_softplus(to_f(proj[t * proj_stride + a_off + h]) + dt_bias[h]));
+        }
+    }
+    const int unit = blockIdx.y * kPrepUnits + warp;
+    if (unit >= 2 * G + H) return;
+    const bool is_v = unit >= 2 * G;
+    const int n = is_v ? dv : d, c0 = is_v ? 2 * G * d + (unit - 2 * G) * dv : unit * d;
     // input of channel c at the portion's offset i (negative: before this portion, from the state row or zero)
     auto input = [&](int i, int c) -> float {
         if (i >= 0) return to_f(proj[(long)(start + i) * proj_stride + qkv_off + c]);
         return rd >= 0 ? state[(long)rd * state_stride + conv_off + (long)(back + i) * C + c] : 0.f;
     };
-    for (int c = tid; c < C; c += blockDim.x) {
-        float y = 0.f;
-        for (int j = 0; j < taps; j++) y = fmaf(to_f(conv_w[(long)c * taps + j]), input(off - back + j, c), y);
-        y = act_silu(y);
-        ys[c] = y;
-        if (c >= 2 * G * d) vv[t * (long)(H * dv) + (c - 2 * G * d)] = y;
-    }
-    if (off == len - 1 && wr >= 0) {
-        for (int i = tid; i < back * C; i += blockDim.x) {
-            const int j = i / C, c = i - j * C;
-            state[(long)wr * state_stride + conv_off + i] = input(len - back + j, c);
+    float y[kPrepPerLane];
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < kPrepPerLane; e++) {
+        const int c = c0 + lane + 32 * e;
+        y[e] = 0.f;
+        if (lane + 32 * e < n) {
+            float a = 0.f;
+            for (int j = 0; j < taps; j++) a = fmaf(to_f(conv_w[(long)c * taps + j]), input(off - back + j, c), a);
+            y[e] = act_silu(a);
+            ss += y[e] * y[e];
         }
     }
-    if (tid < H) {
-        beta[t * H + tid] = dr_sigmoid(to_f(proj[t * proj_stride + b_off + tid]));
-        decay[t * H + tid] = expf(-expf(a_log[tid]) * dr_softplus(to_f(proj[t * proj_stride + a_off + tid]) + dt_bias[tid]));
+    if (off == len - 1 && wr >= 0) {
+        for (int j = 0; j < back; j++)
+            for (int i = lane; i < n; i += 32) state[(long)wr * state_stride + conv_off + (long)j * C + c0 + i] = input(len - back + j, c0 + i);
     }
-    __syncthreads();
-    const float q_scale = 1.0f / sqrtf((float)d);
-    for (int hh = warp; hh < 2 * G; hh += nw) {
-        const float* src = ys + (long)hh * d;
-        float ss = 0.f;
-        for (int i = lane; i < d; i += 32) ss += src[i] * src[i];
+    float mul = 1.f;
+    if (!is_v) {
         ss = warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss + unit_eps) * (hh < G ? q_scale : 1.0f);
-        float* dst = hh < G ? qn + (t * G + hh) * d : kn + (t * G + hh - G) * d;
-        for (int i = lane; i < d; i += 32) dst[i] = src[i] * inv;
+        mul = 1.0f / sqrtf(ss + unit_eps) * (unit < G ? 1.0f / sqrtf((float)d) : 1.0f);
     }
+    float* dst = is_v ? vv + t * (long)(H * dv) + (unit - 2 * G) * dv : (unit < G ? qn + (t * G + unit) * d : kn + (t * G + unit - G) * d);
+#pragma unroll
+    for (int e = 0; e < kPrepPerLane; e++)
+        if (lane + 32 * e < n) dst[lane + 32 * e] = y[e] * mul;
 }
 
 // ------------------------------------------------------------------------------------------------ the recurrence
@@ -185,24 +197,21 @@ using namespace ktb;
 extern "C" int ktb200_delta_prep(const void* proj, long proj_stride, int qkv_off, int b_off, int a_off, const void* conv_w, int taps, const float* a_log, const float* dt_bias,
                                  int heads, int kv_heads, int dim, int vdim, float unit_eps, const int* seq_of, const int* seqs, int seqs_stride, float* state, long state_stride,
                                  float* qn, float* kn, float* vv, float* beta, float* decay, int n_tokens, int dtype, void* stream) {
-    if (!proj || !conv_w || !a_log || !dt_bias || !seq_of || !seqs || !state || !qn || !kn || !vv || !beta || !decay || heads <= 0 || heads > 256 || kv_heads <= 0 ||
-        heads % kv_heads || dim <= 0 || vdim <= 0 || taps < 1) {
-        set_error("delta_prep: bad argument (heads <= 256)");
+    if (!proj || !conv_w || !a_log || !dt_bias || !seq_of || !seqs || !state || !qn || !kn || !vv || !beta || !decay || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
+        dim <= 0 || dim > 32 * kPrepPerLane || vdim <= 0 || vdim > 32 * kPrepPerLane || taps < 1) {
+        set_error("delta_prep: bad argument (head sizes <= %d)", 32 * kPrepPerLane);
         return KTB200_EINVAL;
     }
     if (n_tokens <= 0) return KTB200_OK;
-    const size_t C = (size_t)2 * kv_heads * dim + (size_t)heads * vdim, smem = C * sizeof(float);
-    if (smem > 200 * 1024) { set_error("delta_prep: too many channels for shared memory"); return KTB200_EINVAL; }
     const long conv_off = (long)heads * dim * vdim;
+    const dim3 grid(n_tokens, (2 * kv_heads + heads + kPrepUnits - 1) / kPrepUnits);
     if (dtype == KTB200_TYPE_BF16) {
         using T = __nv_bfloat16;
-        GRANT_SMEM(delta_prep_kernel<T>, smem);
-        delta_prep_kernel<T><<<n_tokens, 256, smem, (cudaStream_t)stream>>>((const T*)proj, proj_stride, qkv_off, b_off, a_off, (const T*)conv_w, taps, a_log, dt_bias, heads, kv_heads,
+        delta_prep_kernel<T><<<grid, kPrepUnits * 32, 0, (cudaStream_t)stream>>>((const T*)proj, proj_stride, qkv_off, b_off, a_off, (const T*)conv_w, taps, a_log, dt_bias, heads, kv_heads,
                                                                             dim, vdim, unit_eps, seq_of, seqs, seqs_stride, state, state_stride, conv_off, qn, kn, vv, beta, decay);
     } else if (dtype == KTB200_TYPE_F32) {
         using T = float;
-        GRANT_SMEM(delta_prep_kernel<T>, smem);
-        delta_prep_kernel<T><<<n_tokens, 256, smem, (cudaStream_t)stream>>>((const T*)proj, proj_stride, qkv_off, b_off, a_off, (const T*)conv_w, taps, a_log, dt_bias, heads, kv_heads,
+        delta_prep_kernel<T><<<grid, kPrepUnits * 32, 0, (cudaStream_t)stream>>>((const T*)proj, proj_stride, qkv_off, b_off, a_off, (const T*)conv_w, taps, a_log, dt_bias, heads, kv_heads,
                                                                             dim, vdim, unit_eps, seq_of, seqs, seqs_stride, state, state_stride, conv_off, qn, kn, vv, beta, decay);
     } else {
         set_error("delta_prep: dtype must be bf16 or f32");

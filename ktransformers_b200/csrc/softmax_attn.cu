@@ -20,7 +20,8 @@
 namespace ktb {
 
 // ------------------------------------------------------------------------------------------------ rotation, unit rms, value blend, cache write
-// One CTA per token, a warp per head (query heads first, then key heads).
+// One CTA per token, a warp per head (query heads first, then key heads).  The token's rot_dims / 2 angles are turned into
+// (cos, sin) once per CTA (fp64 angle and sincos, kept as fp32) and shared by all heads.
 constexpr int kPrepMaxPerLane = 8;      // head size <= 256
 template <typename T>
 __global__ void __launch_bounds__(256) rope_norm_cache_write_kernel(const T* __restrict__ proj, long proj_stride, int q_off, int k_off, int v_off, int H, int G, int d, int dv,
@@ -28,9 +29,16 @@ __global__ void __launch_bounds__(256) rope_norm_cache_write_kernel(const T* __r
                                                                     const T* __restrict__ v_other, long v_other_stride, const float* __restrict__ blend,
                                                                     const int* __restrict__ pos, const int* __restrict__ slot, const int* __restrict__ page_table,
                                                                     int max_pages, int page_size, T* __restrict__ cache, T* __restrict__ q_out) {
+    __shared__ float2 turn[16 * kPrepMaxPerLane];      // (cos, sin) of the token's angles
     const long t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const int p = pos[t];
+    const int p = pos[t], half = rot_dims >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        double sn, cs;
+        sincos((double)p * inv_freq[i], &sn, &cs);
+        turn[i] = make_float2((float)cs, (float)sn);
+    }
+    __syncthreads();
     const T* row = proj + t * proj_stride;
     const long crow = ((long)page_table[(long)slot[t] * max_pages + (p / page_size) % max_pages] * page_size + p % page_size) * ((long)G * (d + dv));
     for (int hh = warp; hh < H + G; hh += nw) {
@@ -44,7 +52,12 @@ __global__ void __launch_bounds__(256) rope_norm_cache_write_kernel(const T* __r
             r[e] = 0.f;
             if (i < d) {
                 float v = to_f(src[i]);
-                if (i < rot_dims) v = rot_turn(v, to_f(src[rot_partner(i, rot_dims, rot_layout)]), i, rot_dims, rot_layout, p, inv_freq);
+                if (i < rot_dims) {
+                    const float other = to_f(src[rot_partner(i, rot_dims, rot_layout)]);
+                    const bool second = rot_layout == kRotHalves ? i >= half : (i & 1);
+                    const float2 cs = turn[rot_layout == kRotHalves ? (second ? i - half : i) : (i >> 1)];
+                    v = second ? v * cs.x + other * cs.y : v * cs.x - other * cs.y;
+                }
                 r[e] = v;
                 s += v * v;
             }
@@ -384,30 +397,34 @@ __global__ void __launch_bounds__(kMmaRows * 2, D16MAX <= 4 ? 4 : 3) window_soft
     }
 }
 
-// one warp per (token, head): the parts' weights exp(m_s - m) / l (parts without a key have m = -inf and weigh nothing), then
-// the columns in parallel, parts in order
+// one CTA of 128 threads per (token, head): the parts' weights exp(m_s - m) / l once in shared memory (parts without a key have
+// m = -inf and weigh nothing), then the columns in parallel, parts in order
+constexpr int kMergeMaxSplits = 128;
 template <typename T>
-__global__ void __launch_bounds__(256) softmax_merge_kernel(const float* __restrict__ partial, int splits, T* __restrict__ out, long n_rows, int dv) {
-    const int lane = threadIdx.x & 31;
-    for (long row = blockIdx.x * (long)(blockDim.x >> 5) + (threadIdx.x >> 5); row < n_rows; row += (long)gridDim.x * (blockDim.x >> 5)) {
-        const float* part = partial + row * splits * (dv + 2);
-        float m = -INFINITY;
-        for (int s = lane; s < splits; s += 32) m = fmaxf(m, part[(long)s * (dv + 2)]);
-        m = warp_max(m);
-        float l = 0.f;
-        for (int s = lane; s < splits; s += 32) {
-            const float ms = part[(long)s * (dv + 2)];
-            if (ms > -INFINITY) l += part[(long)s * (dv + 2) + 1] * expf(ms - m);
-        }
-        l = warp_sum(l);
-        for (int c = lane; c < dv; c += 32) {
-            float a = 0.f;
-            for (int s = 0; s < splits; s++) {
-                const float ms = part[(long)s * (dv + 2)];
-                if (ms > -INFINITY) a = fmaf(expf(ms - m), part[(long)s * (dv + 2) + 2 + c], a);
-            }
-            out[row * dv + c] = from_f<T>(a / l);
-        }
+__global__ void __launch_bounds__(128) softmax_merge_kernel(const float* __restrict__ partial, int splits, T* __restrict__ out, int dv) {
+    __shared__ float wgt[kMergeMaxSplits];
+    __shared__ float red[4];
+    const long row = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* part = partial + row * splits * (dv + 2);
+    const float ms = tid < splits ? part[(long)tid * (dv + 2)] : -INFINITY;
+    const float ls = tid < splits ? part[(long)tid * (dv + 2) + 1] : 0.f;
+    float m = warp_max(ms);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    __syncthreads();
+    const float e = ms > -INFINITY ? expf(ms - m) : 0.f;
+    float l = warp_sum(ls * e);
+    if (lane == 0) red[warp] = l;
+    __syncthreads();
+    l = (red[0] + red[1]) + (red[2] + red[3]);
+    if (tid < splits) wgt[tid] = e / l;
+    __syncthreads();
+    for (int c = tid; c < dv; c += 128) {
+        float a = 0.f;
+        for (int s = 0; s < splits; s++) a = fmaf(wgt[s], part[(long)s * (dv + 2) + 2 + c], a);
+        out[row * dv + c] = from_f<T>(a);
     }
 }
 
@@ -467,8 +484,8 @@ extern "C" int ktb200_window_softmax_attn(const void* q, int heads, int kv_heads
         return KTB200_EINVAL;
     }
     if (n_tokens <= 0) return KTB200_OK;
+    if (splits > kMergeMaxSplits) { set_error("window_softmax_attn: at most %d splits", kMergeMaxSplits); return KTB200_EINVAL; }
     const long rows = (long)n_tokens * heads;
-    const long merge_blocks = (rows + 7) / 8;
     if (allow_tensor_cores && seqs && n_seqs > 0 && ktb200_window_softmax_attn_uses_tensor_cores(heads, kv_heads, dim, vdim, dtype)) {
         using B = __nv_bfloat16;
         const int RH = mma_heads_per_tile(heads / kv_heads);
@@ -486,7 +503,7 @@ extern "C" int ktb200_window_softmax_attn(const void* q, int heads, int kv_heads
 #undef MMA_LAUNCH
         KTB_LAUNCH_CHECK();
         if (splits > 1) {
-            softmax_merge_kernel<B><<<(int)(merge_blocks < 148 * 8 ? merge_blocks : 148 * 8), 256, 0, (cudaStream_t)stream>>>(workspace, splits, (B*)out, rows, vdim);
+            softmax_merge_kernel<B><<<(unsigned)rows, 128, 0, (cudaStream_t)stream>>>(workspace, splits, (B*)out, vdim);
             KTB_LAUNCH_CHECK();
         }
         return KTB200_OK;
@@ -501,7 +518,7 @@ extern "C" int ktb200_window_softmax_attn(const void* q, int heads, int kv_heads
             splits > 1 ? workspace : nullptr, n_tokens);
         KTB_LAUNCH_CHECK();
         if (splits > 1) {
-            softmax_merge_kernel<T><<<(int)(merge_blocks < 148 * 8 ? merge_blocks : 148 * 8), 256, 0, (cudaStream_t)stream>>>(workspace, splits, (T*)out, rows, vdim);
+            softmax_merge_kernel<T><<<(unsigned)rows, 128, 0, (cudaStream_t)stream>>>(workspace, splits, (T*)out, vdim);
             KTB_LAUNCH_CHECK();
         }
     });

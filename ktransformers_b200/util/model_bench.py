@@ -1,5 +1,6 @@
 """Throughput and per-kernel rooflines of a step-function model at layer sizes of real models, with random weights, beside
-the closest existing model's kernels at equal size (`bench.py --model lekapel`, `bench.py --model mabidra`).
+the closest existing model's kernels at equal size (`bench.py --model lekapel`, `bench.py --model mabidra`,
+`bench.py --model zivulix`).
 
 Two parts:
   * end to end through the Engine (scheduler, paged cache, step function): prompt tokens/s for a long prompt cut into portions,
@@ -55,8 +56,41 @@ def make_mabidra_config(s):
             "loop": {"start": s["loop"][0], "stop": s["loop"][1], "times": s["loop"][2]}}
 
 
+ZIVULIX_SIZES = {
+    # the same widths and feed-forward sizes as SIZES, every feed-forward dense; A: soft-max window attention over grouped heads, D: gated
+    # delta rule, L: latent attention at DeepSeek's latent sizes.  The closest existing model at equal size is Mabidra with sigmoid
+    # attention where this has A or L and gated linear attention where this has D, the same dense feed-forward in every layer, no loop.
+    "2k-wide": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, d_heads=16, d_kv_heads=8, d_dim=128, d_vdim=128, conv=4, l_heads=16, dense_ff=8192,
+                    vocab=32768, order="ADLAD", ctx=2048, rank=64),
+    "v3-layer": dict(width=7168, heads=64, kv_heads=8, dim=128, vdim=128, window=4096, d_heads=56, d_kv_heads=28, d_dim=128, d_vdim=128, conv=4, l_heads=128, dense_ff=18432,
+                     vocab=32768, order="ADL", ctx=4096, rank=128),
+}
+
+
+def make_zivulix_config(s):
+    attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5, "softcap": 50.0, "mask": {"size": s["window"]},
+            "rot": {"base": 10000.0, "dims": s["dim"] // 2, "scaling": {"factor": 8.0}}, "v_mix": True}
+    delta = {"heads": s["d_heads"], "kv_heads": s["d_kv_heads"], "dim": s["d_dim"], "vdim": s["d_vdim"], "conv": s["conv"]}
+    latent = {"heads": s["l_heads"], "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}
+    kinds = {"A": ("attention", attn), "D": ("delta", delta), "L": ("latent_attention", latent)}
+    return {"architecture": "Zivulix", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "layers": [{"type": kinds[c][0], "mixer": kinds[c][1], "mlp": {"kind": "dense", "ff": s["dense_ff"]}} for c in s["order"]]}
+
+
+def make_mabidra_dense_config(s):
+    """Mabidra at the sizes of a Zivulix size entry: sigmoid attention for A and L, gated linear attention for D, dense feed-forwards"""
+    attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5, "bias_max": 1024, "q_temp": {"coef": 0.1, "every": 512}}
+    gla = {"heads": s["d_heads"], "dim": s["d_dim"], "vdim": s["d_vdim"], "tau": 16.0}
+    return {"architecture": "Mabidra", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5, "groups": 4}, "embedding": {"scale": 1.0},
+            "layers": [{"type": "gla" if c == "D" else "attention", "mixer": gla if c == "D" else attn, "mlp": {"kind": "dense", "ff": s["dense_ff"]}} for c in s["order"]]}
+
+
 def random_model(cfg_dict, dtype=torch.bfloat16, device="cuda", size=None):
-    if cfg_dict["architecture"] == "Mabidra":
+    if cfg_dict["architecture"] == "Zivulix":
+        from ..models.configuration_zivulix import ZivulixConfig
+        from ..models.modeling_zivulix import ZivulixForCausalLM
+        model = ZivulixForCausalLM(ZivulixConfig.from_dict(cfg_dict), dtype=dtype, device=device)
+    elif cfg_dict["architecture"] == "Mabidra":
         from ..models.configuration_mabidra import MabidraConfig
         from ..models.modeling_mabidra import MabidraForCausalLM
         from ..operators.attention import distance_bias_table
@@ -112,8 +146,14 @@ def timed(fn, flush, iters=10, warmup=3):
 
 def engine_leg(name, size, flush, steps, warmup, family="lekapel"):
     from .engine import Engine
-    cfg = make_config(size) if family == "lekapel" else make_mabidra_config(size)
+    cfg = {"lekapel": make_config, "mabidra": make_mabidra_config, "zivulix": make_zivulix_config, "mabidra-dense": make_mabidra_dense_config}[family](size)
     model = random_model(cfg, size=size)
+    if family == "zivulix":      # norm weights are zero-centred, decays and the value blend inside their usual ranges
+        for pname, p in model.named_parameters():
+            if pname.endswith("weight") or pname.endswith("vmix") or pname.endswith("dt_bias"):
+                p.data.sub_(1.0)
+            if pname.endswith("a_log"):
+                p.data.sub_(3.0)
     prompt_len, chunk, ctx = 4096, 2048, min(4096, size["window"] * 2) if family == "lekapel" else size["ctx"]
     eng = Engine(model, max_tokens=8 * (ctx + 64) + prompt_len, max_slots=9, max_step_tokens=chunk)
     g = torch.Generator().manual_seed(0)
@@ -400,10 +440,186 @@ def mabidra_kernel_leg(flush, peak_gbs, peak_tflops):
     return rows
 
 
+def zivulix_kernel_leg(flush, peak_gbs, peak_tflops):
+    """The kernels of the Zivulix operators at real layer sizes (bf16), each beside the like kernel of the Mabidra path."""
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    seq = native.seq_lib()
+    S = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+    rows = []
+    g = torch.Generator(device=dev).manual_seed(7)
+    rn = lambda *s, dt=bf: torch.randn(*s, generator=g, device=dev, dtype=torch.float32).to(dt)
+
+    def row(kernel, what, ms, nbytes=None, flops=None, peer=None):
+        r = {"kernel": kernel, "case": what, "us": ms * 1e3}
+        progress(f"{kernel} {what}: {ms * 1e3:.1f} us")
+        if nbytes is not None:
+            r.update(GBps=nbytes / ms / 1e6, frac_of_measured_hbm=nbytes / ms / 1e6 / peak_gbs)
+        if flops is not None:
+            r.update(TFLOPs=flops / ms / 1e9, frac_of_measured_bf16=flops / ms / 1e9 / peak_tflops)
+        if peer:
+            r["closest"] = peer
+        rows.append(r)
+
+    def peer_of(kernel, ms, nbytes=None, flops=None):
+        r = {"kernel": kernel, "us": ms * 1e3}
+        if nbytes is not None:
+            r["frac_of_measured_hbm"] = nbytes / ms / 1e6 / peak_gbs
+        if flops is not None:
+            r.update(TFLOPs=flops / ms / 1e9, frac_of_measured_bf16=flops / ms / 1e9 / peak_tflops)
+        return r
+
+    D = 7168
+    for T in (1, 8, 2048):      # residual sum + norm of the added term, the sum rounded for the next GEMM  vs  residual sum + two grouped norms
+        x, y, w1, w2 = rn(T, D, dt=torch.float32), rn(T, D), rn(D), rn(D)
+        xo, h = torch.empty_like(x), torch.empty(T, D, dtype=bf, device=dev)
+        ours = timed(lambda: native.check_seq(seq.ktb200_group_rmsnorm_sandwich(x.data_ptr(), y.data_ptr(), 30, w1.data_ptr(), None, xo.data_ptr(), None, h.data_ptr(), 1, 1e-6, 1.0,
+                                                                                T, D, 30, S())), flush)
+        ms = timed(lambda: native.check_seq(seq.ktb200_group_rmsnorm_sandwich(x.data_ptr(), y.data_ptr(), 30, w1.data_ptr(), None, xo.data_ptr(), w2.data_ptr(), h.data_ptr(), 4, 1e-5,
+                                                                              0.0, T, D, 30, S())), flush)
+        nb = T * D * (4 + 2 + 4 + 2)
+        row("sandwich_norm_kernel (zero-centred weights, plain h)", f"T={T} width={D}", ours, nbytes=nb, peer=peer_of("sandwich_norm_kernel (two grouped norms)", ms, nb))
+
+    # ---- attention: 64 query heads on 8 key/value heads of 128 + 128 values, as the Mabidra attention beside it
+    H, G, d, dv, PAGE = 64, 8, 128, 128, 64
+    cw, n_in = G * (d + dv), (64 + 8) * 128 + 8 * 128
+    inv = torch.arange(d // 4, dtype=torch.float64, device=dev).mul(-4.0 / d).exp2() / 8.0
+    lam = torch.tensor([0.3], device=dev)
+    for T in (8, 2048):         # rotation + unit rms + value blend + cache write  vs  per-head norms + temperature + cache write
+        pages = (T + PAGE - 1) // PAGE
+        proj, vo, cache, qo = rn(T, n_in), rn(T, G * dv), rn(pages + 1, PAGE, cw), torch.empty(T, H, d, dtype=bf, device=dev)
+        ptab = torch.arange(pages, dtype=torch.int32, device=dev).reshape(1, pages)
+        pos, slot = torch.arange(T, dtype=torch.int32, device=dev), torch.zeros(T, dtype=torch.int32, device=dev)
+        ours = timed(lambda: native.check_seq(seq.ktb200_rope_norm_cache_write(proj.data_ptr(), n_in, 0, H * d, (H + G) * d, H, G, d, dv, d // 2, 1, inv.data_ptr(), 1, 1e-6,
+                                                                               vo.data_ptr(), G * dv, lam.data_ptr(), pos.data_ptr(), slot.data_ptr(), ptab.data_ptr(), pages, PAGE,
+                                                                               cache.data_ptr(), qo.data_ptr(), T, 30, S())), flush)
+        qw, kw = rn(d), rn(d)
+        ms = timed(lambda: native.check_seq(seq.ktb200_qk_norm_cache_write(proj.data_ptr(), n_in, H, G, d, dv, qw.data_ptr(), kw.data_ptr(), 1e-5, 0.1, 512, pos.data_ptr(),
+                                                                           slot.data_ptr(), ptab.data_ptr(), pages, PAGE, cache.data_ptr(), qo.data_ptr(), T, 30, S())), flush)
+        nb = T * (n_in + H * d + cw) * 2
+        row("rope_norm_cache_write_kernel", f"T={T} heads={H}/{G} dim={d}", ours, nbytes=nb + T * G * dv * 2, peer=peer_of("qk_norm_cache_write_kernel", ms, nb))
+
+    bias, hb = rn(H, 1026, dt=torch.float32), rn(H, dt=torch.float32)
+    from ..models.configuration_mabidra import SigmoidAttentionSpec
+    from ..models.configuration_zivulix import CappedWindowAttentionSpec
+    from ..operators.attention import KCappedWindowAttention, KSigmoidBiasAttention
+    for B, ctx in ((1, 4096), (8, 4096), (1, 32768)):
+        pages = (ctx + PAGE - 1) // PAGE
+        cache = rn(B * pages + 1, PAGE, cw)
+        ptab = torch.arange(B * pages, dtype=torch.int32, device=dev).reshape(B, pages)
+        q, gate, out = rn(B, H, d), rn(B, H), torch.empty(B, H * dv, dtype=bf, device=dev)
+        pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+        slot = torch.arange(B, dtype=torch.int32, device=dev)
+        seqs = torch.tensor([list(range(B)), [1] * B, [-1] * B, [-1] * B], dtype=torch.int32, device=dev)
+        mine = type("X", (), {"spec": CappedWindowAttentionSpec(H, G, d, dv, d ** -0.5, 50.0, ctx, None, True, True)})()
+        theirs = type("X", (), {"spec": SigmoidAttentionSpec(H, G, d, dv, d ** -0.5, 1024.0, 0.1, 512)})()
+        sp = KSigmoidBiasAttention.pick_splits(theirs, B, ctx, B, True)
+        ws = torch.empty(max(1, seq.ktb200_sigmoid_bias_attn_workspace(B, H, dv, sp) // 4), device=dev)
+        ms = timed(lambda: native.check_seq(seq.ktb200_sigmoid_bias_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, bias.data_ptr(), bias.shape[1], hb.data_ptr(), pos.data_ptr(), slot.data_ptr(),
+                                                                         seqs.data_ptr(), B, B, ptab.data_ptr(), pages, PAGE, cache.data_ptr(), gate.data_ptr(), H, out.data_ptr(), B, sp,
+                                                                         ws.data_ptr(), 30, 1, S())), flush)
+        nb = B * ctx * cw * 2
+        peer = peer_of("sigmoid_attn_mma_kernel (+merge)", ms, nb)
+        for tc in (1, 0):
+            splits = KCappedWindowAttention.pick_splits(mine, B, ctx, B, bool(tc))
+            ws2 = torch.empty(max(1, seq.ktb200_window_softmax_attn_workspace(B, H, dv, splits) // 4), device=dev)
+            fn = lambda: native.check_seq(seq.ktb200_window_softmax_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, 50.0, ctx, pos.data_ptr(), slot.data_ptr(), seqs.data_ptr(), B, B,
+                                                                         ptab.data_ptr(), pages, PAGE, cache.data_ptr(), out.data_ptr(), B, splits, ws2.data_ptr(), 30, tc, S()))
+            row("window_softmax_attn_mma_kernel (+merge)" if tc else "window_softmax_attn_kernel (+merge), CUDA cores", f"decode B={B} ctx={ctx} heads={H}/{G} splits={splits}",
+                timed(fn, flush), nbytes=nb, peer=peer)
+    T, ctx = 2048, 4096
+    pages = ctx // PAGE
+    cache = rn(pages + 1, PAGE, cw)
+    ptab = torch.arange(pages, dtype=torch.int32, device=dev).reshape(1, pages)
+    q, gate, out = rn(T, H, d), rn(T, H), torch.empty(T, H * dv, dtype=bf, device=dev)
+    pos = torch.arange(ctx - T, ctx, dtype=torch.int32, device=dev)
+    slot = torch.zeros(T, dtype=torch.int32, device=dev)
+    keys = float(sum(range(ctx - T + 1, ctx + 1)))
+    seqs = torch.tensor([[0], [T], [-1], [-1]], dtype=torch.int32, device=dev)
+    fl = keys * H * (d + dv) * 2
+    ms = timed(lambda: native.check_seq(seq.ktb200_sigmoid_bias_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, bias.data_ptr(), bias.shape[1], hb.data_ptr(), pos.data_ptr(), slot.data_ptr(),
+                                                                     seqs.data_ptr(), 1, 1, ptab.data_ptr(), pages, PAGE, cache.data_ptr(), gate.data_ptr(), H, out.data_ptr(), T, 1, None, 30,
+                                                                     1, S())), flush, iters=5, warmup=2)
+    peer = peer_of("sigmoid_attn_mma_kernel", ms, flops=fl)
+    fn = lambda tc, win: native.check_seq(seq.ktb200_window_softmax_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, 50.0, win, pos.data_ptr(), slot.data_ptr(), seqs.data_ptr(), 1, 1,
+                                                                         ptab.data_ptr(), pages, PAGE, cache.data_ptr(), out.data_ptr(), T, 1, None, 30, tc, S()))
+    row("window_softmax_attn_mma_kernel", f"prompt portion T={T} positions {ctx - T}..{ctx - 1} heads={H}/{G}, every earlier key in sight", timed(lambda: fn(1, ctx), flush, iters=5, warmup=2),
+        flops=fl, peer=peer)
+    row("window_softmax_attn_mma_kernel", f"the same, window 1024", timed(lambda: fn(1, 1024), flush, iters=5, warmup=2), flops=float(T) * 1024 * H * (d + dv) * 2)
+    row("window_softmax_attn_kernel, CUDA cores", f"prompt portion T={T} positions {ctx - T}..{ctx - 1} heads={H}/{G}", timed(lambda: fn(0, ctx), flush, iters=2, warmup=1), flops=fl)
+
+    # ---- the gated delta rule: decode reads and writes the fp32 state once (bytes); a prompt portion is a chain of T dependent steps
+    DH, DG, dd, ddv, taps = 56, 28, 128, 128, 4
+    C_ = 2 * DG * dd + DH * ddv
+    n_in = C_ + DH * ddv + 2 * DH
+    n_in = (n_in + 7) // 8 * 8
+    sw = DH * dd * ddv + (taps - 1) * C_
+    GH, gd, gdv = 56, 128, 128
+    g_in = 2 * GH * gd + 2 * GH * gdv
+    for B, T in ((1, 1), (8, 1), (1, 2048)):
+        proj, cwt = rn(B * T, n_in), rn(C_, taps)
+        al, dtb = rn(DH, dt=torch.float32) - 3.0, rn(DH, dt=torch.float32)
+        state = torch.zeros(2 * B, sw, device=dev)
+        f32 = lambda *s: torch.empty(*s, device=dev)
+        qn, kn, vv, be, de, o = f32(B * T, DG * dd), f32(B * T, DG * dd), f32(B * T, DH * ddv), f32(B * T, DH), f32(B * T, DH), f32(B * T, DH * ddv)
+        seqs = torch.tensor([[i * T for i in range(B)], [T] * B, [2 * i for i in range(B)], [2 * i + 1 for i in range(B)]], dtype=torch.int32, device=dev)
+        seq_of = torch.arange(B, dtype=torch.int32, device=dev).repeat_interleave(T)
+        prep = lambda: native.check_seq(seq.ktb200_delta_prep(proj.data_ptr(), n_in, 0, C_ + DH * ddv, C_ + DH * ddv + DH, cwt.data_ptr(), taps, al.data_ptr(), dtb.data_ptr(), DH, DG, dd,
+                                                              ddv, 1e-6, seq_of.data_ptr(), seqs.data_ptr(), B, state.data_ptr(), sw, qn.data_ptr(), kn.data_ptr(), vv.data_ptr(),
+                                                              be.data_ptr(), de.data_ptr(), B * T, 30, S()))
+        scan = lambda: native.check_seq(seq.ktb200_delta_scan(qn.data_ptr(), kn.data_ptr(), vv.data_ptr(), be.data_ptr(), de.data_ptr(), DH, DG, dd, ddv, seqs.data_ptr(), B, B,
+                                                              state.data_ptr(), sw, o.data_ptr(), S()))
+        prep()
+        gproj, z, zb = rn(B * T, g_in), rn(B * T, GH * gd), rn(GH * gd)
+        gstate, go = torch.zeros(2 * B, GH * gd * gdv, device=dev), torch.empty(B * T, GH * gdv, device=dev)
+        gla = lambda: native.check_seq(seq.ktb200_gla_scan(gproj.data_ptr(), g_in, 0, GH * gd, 2 * GH * gd, z.data_ptr(), GH * gd, zb.data_ptr(), 16.0, GH, gd, gdv, seqs.data_ptr(), B, B,
+                                                           B * T, gstate.data_ptr(), go.data_ptr(), 30, S()))
+        it = 5 if T > 1 else 10
+        ms_prep, ms_scan, ms_gla = timed(prep, flush, iters=it), timed(scan, flush, iters=it), timed(gla, flush, iters=it)
+        row("delta_prep_kernel", f"B={B} T={T} heads={DH}/{DG} taps={taps}", ms_prep, nbytes=B * T * (C_ * 2 + C_ * 4 + 2 * DH * 4) + B * (taps - 1) * C_ * 8)
+        if T == 1:
+            nb = B * DH * dd * ddv * 8
+            row("delta_scan_kernel", f"decode B={B} heads={DH}/{DG} dim={dd} vdim={ddv}", ms_scan, nbytes=nb, peer=peer_of("gla_scan_kernel", ms_gla, B * GH * gd * gdv * 8))
+        else:
+            fl = float(T) * DH * dd * ddv * 6
+            row("delta_scan_kernel", f"prompt portion T={T} heads={DH}/{DG} dim={dd} vdim={ddv} ({ms_scan * 1e3 / T:.2f} us per token step)", ms_scan, flops=fl,
+                peer=dict(peer_of("gla_scan_kernel", ms_gla, flops=float(T) * GH * gd * gdv * 4), us_per_token_step=ms_gla * 1e3 / T))
+    # ---- activation
+    for T, ff in ((8, 18432), (2048, 18432)):
+        gu, oo, zz, pq = rn(T, 2 * ff), torch.empty(T, ff, dtype=bf, device=dev), rn(T, ff), torch.tensor([0.3, -0.2], device=dev)
+        ours = timed(lambda: native.check_seq(seq.ktb200_gated_act_mul(gu.data_ptr(), oo.data_ptr(), T, ff, 1, 30, S())), flush)
+        ms = timed(lambda: native.check_seq(seq.ktb200_xielu(zz.data_ptr(), oo.data_ptr(), pq.data_ptr(), zz.numel(), 30, S())), flush)
+        row("gated_act_mul_kernel (gelu_tanh)", f"T={T} ff={ff}", ours, nbytes=T * ff * 6, peer=peer_of("xielu_kernel", ms, T * ff * 4))
+    return rows
+
+
+def run_zivulix(args):
+    torch.cuda.set_device(0)
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        m = json.load(open(os.path.join(root, "MEASURED_PEAKS.json")))
+        peak, tf, src = float(m["hbm_gbs"]), float(m["bf16_tflops"]), "measured (MEASURED_PEAKS.json hbm_gbs, bf16_tflops)"
+    except Exception:
+        peak, tf, src = 6650.0, 1590.0, "fallback"
+    flush = Flusher("cuda")
+    n0 = native.seq_lib().ktb200_launch_count()
+    out = {"bench": "zivulix", "dtype": "bf16", "data": "synthetic (random weights and tokens)", "hbm_peak_GBps": peak, "bf16_peak_TFLOPs": tf, "peak_source": src,
+           "timing": "CUDA events, median, 256 MB L2 flush between timed calls", "kernels": [] if getattr(args, "no_kernels", False) else zivulix_kernel_leg(flush, peak, tf),
+           "models": [], "closest_models": []}
+    for name in (args.sizes.split(",") if getattr(args, "sizes", None) else ZIVULIX_SIZES):
+        out["models"].append(engine_leg(name, ZIVULIX_SIZES[name], flush, args.steps, args.warmup, family="zivulix"))
+        torch.cuda.empty_cache()
+        out["closest_models"].append(engine_leg(name, ZIVULIX_SIZES[name], flush, args.steps, args.warmup, family="mabidra-dense"))      # Mabidra at the same sizes, in the same process
+        torch.cuda.empty_cache()
+    out["gpu_launches"] = int(native.seq_lib().ktb200_launch_count() - n0)
+    print(json.dumps(out))
+
+
 def run(args):
-    """`bench.py --model lekapel | mabidra`: prints one JSON line."""
+    """`bench.py --model lekapel | mabidra | zivulix`: prints one JSON line."""
     if args.model == "mabidra":
         return run_mabidra(args)
+    if args.model == "zivulix":
+        return run_zivulix(args)
     torch.cuda.set_device(0)
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     try:
