@@ -68,8 +68,8 @@ ZIVULIX_SIZES = {
 
 
 def make_zivulix_config(s):
-    attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5, "softcap": 50.0, "mask": {"size": s["window"]},
-            "rot": {"base": 10000.0, "dims": s["dim"] // 2, "scaling": {"factor": 8.0}}, "v_mix": True}
+    attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5, "softcap": 30.0, "mask": {"size": s["window"]},
+            "rot": {"base": 10000.0, "dims": s["dim"] // 2, "scaling": {"factor": 4.0}}, "v_mix": True}
     delta = {"heads": s["d_heads"], "kv_heads": s["d_kv_heads"], "dim": s["d_dim"], "vdim": s["d_vdim"], "conv": s["conv"]}
     latent = {"heads": s["l_heads"], "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}
     kinds = {"A": ("attention", attn), "D": ("delta", delta), "L": ("latent_attention", latent)}
@@ -482,7 +482,7 @@ def zivulix_kernel_leg(flush, peak_gbs, peak_tflops):
     # ---- attention: 64 query heads on 8 key/value heads of 128 + 128 values, as the Mabidra attention beside it
     H, G, d, dv, PAGE = 64, 8, 128, 128, 64
     cw, n_in = G * (d + dv), (64 + 8) * 128 + 8 * 128
-    inv = torch.arange(d // 4, dtype=torch.float64, device=dev).mul(-4.0 / d).exp2() / 8.0
+    inv = torch.arange(d // 4, dtype=torch.float64, device=dev).mul(-4.0 / d).exp2() / 4.0
     lam = torch.tensor([0.3], device=dev)
     for T in (8, 2048):         # rotation + unit rms + value blend + cache write  vs  per-head norms + temperature + cache write
         pages = (T + PAGE - 1) // PAGE
@@ -510,7 +510,7 @@ def zivulix_kernel_leg(flush, peak_gbs, peak_tflops):
         pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
         slot = torch.arange(B, dtype=torch.int32, device=dev)
         seqs = torch.tensor([list(range(B)), [1] * B, [-1] * B, [-1] * B], dtype=torch.int32, device=dev)
-        mine = type("X", (), {"spec": CappedWindowAttentionSpec(H, G, d, dv, d ** -0.5, 50.0, ctx, None, True, True)})()
+        mine = type("X", (), {"spec": CappedWindowAttentionSpec(H, G, d, dv, d ** -0.5, 30.0, ctx, None, True, True)})()
         theirs = type("X", (), {"spec": SigmoidAttentionSpec(H, G, d, dv, d ** -0.5, 1024.0, 0.1, 512)})()
         sp = KSigmoidBiasAttention.pick_splits(theirs, B, ctx, B, True)
         ws = torch.empty(max(1, seq.ktb200_sigmoid_bias_attn_workspace(B, H, dv, sp) // 4), device=dev)
@@ -522,7 +522,7 @@ def zivulix_kernel_leg(flush, peak_gbs, peak_tflops):
         for tc in (1, 0):
             splits = KCappedWindowAttention.pick_splits(mine, B, ctx, B, bool(tc))
             ws2 = torch.empty(max(1, seq.ktb200_window_softmax_attn_workspace(B, H, dv, splits) // 4), device=dev)
-            fn = lambda: native.check_seq(seq.ktb200_window_softmax_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, 50.0, ctx, pos.data_ptr(), slot.data_ptr(), seqs.data_ptr(), B, B,
+            fn = lambda: native.check_seq(seq.ktb200_window_softmax_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, 30.0, ctx, pos.data_ptr(), slot.data_ptr(), seqs.data_ptr(), B, B,
                                                                          ptab.data_ptr(), pages, PAGE, cache.data_ptr(), out.data_ptr(), B, splits, ws2.data_ptr(), 30, tc, S()))
             row("window_softmax_attn_mma_kernel (+merge)" if tc else "window_softmax_attn_kernel (+merge), CUDA cores", f"decode B={B} ctx={ctx} heads={H}/{G} splits={splits}",
                 timed(fn, flush), nbytes=nb, peer=peer)
@@ -540,7 +540,7 @@ def zivulix_kernel_leg(flush, peak_gbs, peak_tflops):
                                                                      seqs.data_ptr(), 1, 1, ptab.data_ptr(), pages, PAGE, cache.data_ptr(), gate.data_ptr(), H, out.data_ptr(), T, 1, None, 30,
                                                                      1, S())), flush, iters=5, warmup=2)
     peer = peer_of("sigmoid_attn_mma_kernel", ms, flops=fl)
-    fn = lambda tc, win: native.check_seq(seq.ktb200_window_softmax_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, 50.0, win, pos.data_ptr(), slot.data_ptr(), seqs.data_ptr(), 1, 1,
+    fn = lambda tc, win: native.check_seq(seq.ktb200_window_softmax_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, 30.0, win, pos.data_ptr(), slot.data_ptr(), seqs.data_ptr(), 1, 1,
                                                                          ptab.data_ptr(), pages, PAGE, cache.data_ptr(), out.data_ptr(), T, 1, None, 30, tc, S()))
     row("window_softmax_attn_mma_kernel", f"prompt portion T={T} positions {ctx - T}..{ctx - 1} heads={H}/{G}, every earlier key in sight", timed(lambda: fn(1, ctx), flush, iters=5, warmup=2),
         flops=fl, peer=peer)
