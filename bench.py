@@ -242,6 +242,10 @@ def run_reference_arm(args, rank):
     if rank != 0:
         return
     world = max(1, args.gpus)
+    from oracle.bindings import Ref
+    if not Ref.available():                  # never report this repo's own C restatement under the reference's name
+        print(json.dumps({"impl": "reference", "unavailable": "the unmodified reference is not built here (oracle/_ref is made by `make -C oracle ref` where the reference's sources are present)"}), flush=True)
+        return
     cpu = RefCpuMoe(tokens=world)            # same config as the B200 arm: `world` tokens per step
     for _ in range(args.warmup):
         cpu.token()
