@@ -183,7 +183,8 @@ __global__ void __launch_bounds__(256) window_softmax_attn_kernel(const T* __res
 // rows gathered through the page table, from the first key that the tile's earliest token still sees to its last token's own;
 // S = Q K^T and O += P V are m16n8k16 bf16 MMAs with fp32 accumulators; scale, cap, window and causal masks, running maximum and
 // sum in fp32 registers (a row's maximum over the four threads that hold it); the weights go to the second product as bf16.
-// grid (tile bound, G * head blocks, splits); tiles are found from the per-sequence rows `seqs`.
+// grid (tile bound, G * head blocks, splits); tiles are found from the per-sequence rows `seqs`.  Held to 128 registers (a few bytes of
+// spills at head size 128) so that four CTAs share an SM: decode-shaped launches are bound by the copies in flight per SM.
 constexpr int kMmaRows = 64, kMmaKeys = 32, kMmaPad = 8;
 __device__ __forceinline__ float cap_score_fast(float s, float two_over_cap, float softcap) {
     // c tanh(s / c) as c (1 - 2 / (exp(2 s / c) + 1)), c = softcap: absolute error of a few 1e-7 of the cap
@@ -191,7 +192,7 @@ __device__ __forceinline__ float cap_score_fast(float s, float two_over_cap, flo
 }
 
 template <int D16MAX, int DV16MAX>
-__global__ void __launch_bounds__(kMmaRows * 2, D16MAX <= 4 ? 4 : 3) window_softmax_attn_mma_kernel(
+__global__ void __launch_bounds__(kMmaRows * 2, 4) window_softmax_attn_mma_kernel(
     const __nv_bfloat16* __restrict__ q, int H, int G, int d, int dv, float scale, float softcap, int window, const int* __restrict__ pos, const int* __restrict__ slot,
     const int* __restrict__ seqs, int seqs_stride, int n_seqs, int RH, const int* __restrict__ page_table, int max_pages, int page_size, const __nv_bfloat16* __restrict__ cache,
     __nv_bfloat16* __restrict__ out, float* __restrict__ partial) {
