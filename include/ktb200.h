@@ -212,6 +212,8 @@ typedef struct ktb200_gate_config {
  * logits_dev optional fp32 [qlen][n_experts] scratch/out (NULL -> internal). */
 int ktb200_moe_gate_forward(const ktb200_gate_config* cfg, int qlen, const void* x_dev, int64_t* idx_dev,
                             float* w_dev, float* logits_dev, const int* bsz_tensor_dev, void* stream);
+/* The same selection on logits [qlen][n_experts] fp32 that the caller computed (one CTA per token: prompt-sized batches). */
+int ktb200_moe_gate_select(const ktb200_gate_config* cfg, int qlen, const float* logits_dev, int64_t* idx_dev, float* w_dev, void* stream);
 
 /* Expert-parallel shard form of ktb200_moe_forward_shared: `partial_out` [qlen][hidden] receives the routed partial sums
  * of the experts this shard owns (hidden_type of the moe handle, fp32 for an exact cross-rank sum), and the shared
@@ -354,7 +356,8 @@ int ktb200_mla_kv_write(void* kv_cache, int page_size, const void* ckv, const vo
  * activations, weights and the cache; norms, angles, scores, the residual sum and all reductions are fp32.  One launch serves
  * a ragged batch: token t belongs to sequence slot[t] at position pos[t].
  *
- * ktb200_group_rmsnorm_shift: x_out = x_in + mult * (a + b) when a or b is given (x_out != x_in), h = RMS norm of the row in
+ * ktb200_group_rmsnorm_shift: x_out = x_in + mult * (a + b) + row_add when a, b or row_add ([width] fp32, the same for every token) is
+ *   given (x_out != x_in), h = RMS norm of the row in
  *   `groups` equal consecutive parts times weight, and with `shift` != NULL  hs_t = h_t + (prev - h_t) * shift  where prev is the
  *   h of row prev_idx[t] of this launch (>= 0), else state row rd_row[t] (>= 0), else zero; h_t is stored to state row
  *   wr_row[t] when >= 0 (the caller double-buffers the state rows so that no launch reads a row it writes).
@@ -371,7 +374,7 @@ int ktb200_mla_kv_write(void* kv_cache, int page_size, const void* ckv, const vo
  * ktb200_experts_gate_up / _down: dense experts [E][ff][width] / [E][width][ff], ids [T][top] int64 and weights [T][top] as
  *   ktb200_moe_gate_forward writes them; act [T*top][ff]; out [T][width] fp32.
  * ------------------------------------------------------------------------------------------ */
-int ktb200_group_rmsnorm_shift(const float* x_in, const void* delta_a, int a_type, const void* delta_b, int b_type, float mult, float* x_out,
+int ktb200_group_rmsnorm_shift(const float* x_in, const void* delta_a, int a_type, const void* delta_b, int b_type, float mult, const float* row_add, float* x_out,
                                const void* weight, int groups, float eps, const void* shift, const int* prev_idx, const int* rd_row,
                                const int* wr_row, float* state, void* h_out, void* hs_out, int n_tokens, int width, int dtype, void* stream);
 int ktb200_latent_prep(const void* proj, long proj_stride, int q_rank, int kv_rank, int rot_dim, int rot_dims, int rot_layout, const double* inv_freq,
@@ -395,17 +398,19 @@ int ktb200_sigmoid_gate_mul(const void* heads, const void* gate, long gate_strid
                             int dtype, void* stream);
 int ktb200_poly_norm(const void* z, void* out, const float* coef, float eps, int n_tokens, int ff, int dtype, void* stream);
 int ktb200_experts_gate_up(const void* x, const int64_t* ids, int top, const void* w_gate, const void* w_up, void* act, int n_tokens,
-                           int width, int ff, int dtype, void* stream);
+                           int width, int ff, int act_kind, float limit, int dtype, void* stream);
 int ktb200_experts_down(const void* act, const int64_t* ids, const float* weights, int top, const void* w_down, float* out, int n_tokens,
                         int width, int ff, int dtype, void* stream);
 /* the same for batches of a few tokens, by expert: each expert's rows are streamed once per `staged` (2 or 4; 0: chosen from the
  *   batch) pairs routed to it instead of once per pair; pair_rows [T*top][width] fp32 is scratch for the per-pair down rows
  *   before the weighted sum in slot order. */
 int ktb200_experts_gate_up_by_expert(const void* x, const int64_t* ids, int top, int n_experts, const void* w_gate, const void* w_up, void* act,
-                                     int n_tokens, int width, int ff, int staged, int dtype, void* stream);
+                                     int n_tokens, int width, int ff, int staged, int act_kind, float limit, int dtype, void* stream);
 int ktb200_experts_down_by_expert(const void* act, const int64_t* ids, const float* weights, int top, int n_experts, const void* w_down,
                                   float* pair_rows, float* out, int n_tokens, int width, int ff, int staged, int dtype, void* stream);
-/* w_gate == NULL in the four calls above: experts of two matrices, act = relu(W_up x)^2.
+/* w_gate == NULL in the four calls above: experts of two matrices, act = relu(W_up x)^2.  Otherwise act_kind picks what becomes of
+ * g = W_gate x and u = W_up x: 0 silu(g) u; 1 gelu(g) u (tanh form); 2 g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit),
+ * u' = clamp(u, -limit, limit).
  *
  * Layers with norms on both sides of every sublayer, sigmoid attention and gated linear attention (csrc/seq_mixers.cu):
  *   ktb200_group_rmsnorm_sandwich   x_out = x_in + gnorm(y) * (w_post + weight_offset) + row_add ; h = gnorm(x_out) * (w_pre + weight_offset).
@@ -443,14 +448,20 @@ int ktb200_gla_scan(const void* proj, long proj_stride, int q_off, int k_off, in
 int ktb200_gla_out(const float* o, const void* norm_w, float eps, const void* gate, long gate_stride, void* out, int n_tokens, int heads,
                    int vdim, int dtype, void* stream);
 int ktb200_xielu(const void* z, void* out, const float* pq, long n, int dtype, void* stream);
-/* out[t][i] = act(gate_up[t][i]) * gate_up[t][ff + i]; act 0: SiLU, 1: GELU in its tanh form */
-int ktb200_gated_act_mul(const void* gate_up, void* out, int n_tokens, int ff, int act, int dtype, void* stream);
+/* out[t][i] = that activation (act, limit as act_kind above) of gate[t * in_stride + i] and up[t * in_stride + i]; rows [gate | up]: up = gate + ff,
+ * in_stride = 2 ff.  ktb200_relu_squared: out = relu(z)^2.  ktb200_softcap: out (fp32) = cap tanh(z / cap). */
+int ktb200_gated_act_mul(const void* gate, const void* up, long in_stride, void* out, int n_tokens, int ff, int act, float limit, int dtype, void* stream);
+int ktb200_relu_squared(const void* z, void* out, long n, int dtype, void* stream);
+int ktb200_softcap(const void* z, float* out, long n, float cap, int dtype, void* stream);
 
 /* Soft-max attention over grouped key/value heads (csrc/softmax_attn.cu) and the gated delta rule (csrc/delta_rule.cu):
  *   ktb200_rope_norm_cache_write   proj rows hold q [H*d] at q_off, k [G*d] at k_off, v [G*dv] at v_off: q and k turn over their first rot_dims
- *                                  columns (rot_layout as above), are divided by sqrt(mean(x^2) + eps) per head when unit_rms, v becomes
- *                                  (1 - blend[0]) v + blend[0] v_other[token] when v_other is given; [k | v] into the paged cache, q into q_out
- *   ktb200_window_softmax_attn     out[t][h] = sum_j softmax_j(cap(scale q.k_j)) v_j over pos - window < j <= pos (window <= 0: all j <= pos),
+ *                                  columns (rot_layout as above), are divided by sqrt(mean(x^2) + eps) per head (qk_norm 1), or over the whole
+ *                                  q (k) row and then multiplied by q_weight [H*d] (k_weight [G*d]) (qk_norm 2; 0: neither), v becomes
+ *                                  (1 - blend[0]) v + blend[0] v_other[token] when v_other is given and is then divided by sqrt(mean(v^2) + eps)
+ *                                  per value head when v_unit_rms; [k | v] into the paged cache, q into q_out
+ *   ktb200_window_softmax_attn     out[t][h] = sum_j softmax_j(cap(scale head_scale[h] q.k_j)) v_j over the keys j <= pos with pos - j < window
+ *                                  (window > 0) and floor(j / chunk) == floor(pos / chunk) (chunk > 0); head_scale NULL: 1;
  *                                  cap(s) = c tanh(s / c), c = softcap (softcap <= 0: none); splits > 1 cuts the key range
  *                                  (workspace: ktb200_window_softmax_attn_workspace bytes)
  *   ktb200_delta_prep              channels [q G*d | k G*d | v H*dv] of proj at qkv_off: causal convolution over `taps` tokens per channel
@@ -460,12 +471,12 @@ int ktb200_gated_act_mul(const void* gate_up, void* out, int n_tokens, int ff, i
  *   ktb200_delta_scan              per portion seqs[0..3][s] and head: M <- a M; r = eta (v - M^T k); M <- M + k r^T; y = M^T q.
  *                                  State rows: [M heads*dim*vdim | conv inputs (taps - 1)*channels] fp32, row stride state_stride; dim, vdim <= 256 */
 int ktb200_rope_norm_cache_write(const void* proj, long proj_stride, int q_off, int k_off, int v_off, int heads, int kv_heads, int dim, int vdim,
-                                 int rot_dims, int rot_layout, const double* inv_freq, int unit_rms, float eps, const void* v_other, long v_other_stride,
-                                 const float* blend, const int* pos, const int* slot, const int* page_table, int max_pages, int page_size, void* cache,
+                                 int rot_dims, int rot_layout, const double* inv_freq, int qk_norm, const void* q_weight, const void* k_weight,
+                                 int v_unit_rms, float eps, const void* v_other, long v_other_stride, const float* blend, const int* pos, const int* slot, const int* page_table, int max_pages, int page_size, void* cache,
                                  void* q_out, int n_tokens, int dtype, void* stream);
 size_t ktb200_window_softmax_attn_workspace(int n_tokens, int heads, int vdim, int splits);
-int ktb200_window_softmax_attn(const void* q, int heads, int kv_heads, int dim, int vdim, float scale, float softcap, int window, const int* pos,
-                               const int* slot, const int* seqs, int seqs_stride, int n_seqs, const int* page_table, int max_pages, int page_size,
+int ktb200_window_softmax_attn(const void* q, int heads, int kv_heads, int dim, int vdim, float scale, const float* head_scale, float softcap,
+                               int window, int chunk, const int* pos, const int* slot, const int* seqs, int seqs_stride, int n_seqs, const int* page_table, int max_pages, int page_size,
                                const void* cache, void* out, int n_tokens, int splits, float* workspace, int dtype, int allow_tensor_cores,
                                void* stream);
 /* whether that call runs tensor-core tiles (bf16, dim and vdim multiples of 16 up to 128, seqs given), and an upper bound of its

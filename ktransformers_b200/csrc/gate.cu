@@ -74,6 +74,13 @@ __global__ void __launch_bounds__(kGateThreads) gate_kernel(const GateParams p) 
     }
 }
 
+// Selection alone, from logits that a GEMM has already made ([T][E] fp32): one CTA per token (grid-stride), for prompt-sized batches.
+__global__ void __launch_bounds__(kGateThreads) gate_select_kernel(const GateParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    for (int t = blockIdx.x; t < p.T; t += gridDim.x)
+        gate_select_token<0>(p, t, reinterpret_cast<float*>(smem_raw), p.idx + (long)t * p.top_k, p.w + (long)t * p.top_k, nullptr);
+}
+
 // per-device scratch: partial sums + ticket
 static float* g_partial[64] = {nullptr};
 static size_t g_partial_cap[64] = {0};
@@ -125,6 +132,30 @@ extern "C" int ktb200_moe_gate_forward(const ktb200_gate_config* c, int qlen, co
     if (smem_sel > smem) smem = smem_sel;
     if (smem > 48 * 1024) KTB_CUDA_CHECK(cudaFuncSetAttribute(gate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     gate_kernel<<<dim3(row_ctas, S), kGateThreads, smem, s>>>(p);
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+/* The selection of ktb200_moe_gate_forward on logits [qlen][E] fp32 computed elsewhere (c->weight and c->hidden_* are not read). */
+extern "C" int ktb200_moe_gate_select(const ktb200_gate_config* c, int qlen, const float* logits, int64_t* idx, float* w, void* stream) {
+    using namespace ktb;
+    if (!c || !logits || !idx || !w) { set_error("null pointer"); return KTB200_EINVAL; }
+    if (qlen <= 0) return KTB200_OK;
+    if (c->n_experts <= 0 || c->n_experts > kGateThreads * kGateEPT || c->top_k <= 0 || c->top_k > 32 || c->top_k > c->n_experts) {
+        set_error("gate: bad shape (E=%d top_k=%d; E<=%d, top_k<=32)", c->n_experts, c->top_k, kGateThreads * kGateEPT);
+        return KTB200_EINVAL;
+    }
+    if (c->n_group < 1 || c->n_group > 32 || c->n_experts % c->n_group || c->topk_group < 1 || c->topk_group > c->n_group) {
+        set_error("gate: bad grouping (n_group=%d topk_group=%d)", c->n_group, c->topk_group);
+        return KTB200_EINVAL;
+    }
+    if (c->scoring < 0 || c->scoring > 2 || c->topk_method < 0 || c->topk_method > 2) { set_error("gate: bad scoring/topk_method"); return KTB200_EINVAL; }
+    GateParams p{nullptr, nullptr, c->hidden_type, c->n_experts, c->hidden_size, qlen, 1, c->top_k, c->n_group, c->topk_group,
+                 c->scoring, c->topk_method, c->norm_topk_prob, c->routed_scaling_factor, c->bias, const_cast<float*>(logits), nullptr,
+                 idx, w, nullptr, nullptr};
+    const size_t smem = ((size_t)2 * c->n_experts + 32 + 4 * kGateWarps) * sizeof(float);
+    const int blocks = qlen < 148 * 16 ? qlen : 148 * 16;
+    gate_select_kernel<<<blocks, kGateThreads, smem, (cudaStream_t)stream>>>(p);
     KTB_LAUNCH_CHECK();
     return KTB200_OK;
 }

@@ -167,7 +167,8 @@ __device__ void gate_select_token(const GateParams& pin, int t, float* sm, int64
             const unsigned mx1 = __reduce_max_sync(0xffffffffu, k1);
             const int wl = __ffs(__ballot_sync(0xffffffffu, k1 == mx1)) - 1;
             const unsigned mx2 = __reduce_max_sync(0xffffffffu, lane == wl ? fkey(a2) : k1);
-            if (lane == 0) gsc[g] = (p.topk_method == 0) ? (fkey_inv(mx1) + fkey_inv(mx2)) : fkey_inv(mx1);
+            // (a group of ONE expert has no second score: its own counts alone)
+            if (lane == 0) gsc[g] = (p.topk_method == 0 && gs > 1) ? (fkey_inv(mx1) + fkey_inv(mx2)) : fkey_inv(mx1);
         }
         gate_sync<BAR>();
         const float fill = (p.topk_method == 0) ? -INFINITY : 0.0f;  // V3 masks with -inf, V2 with 0.0

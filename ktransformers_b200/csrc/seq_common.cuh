@@ -100,6 +100,21 @@ __device__ __forceinline__ float rot_turn(float own, float other, int c, int rot
     return second ? own * (float)cs + other * (float)sn : own * (float)cs - other * (float)sn;
 }
 
+// Gated feed-forward activations, fp32: what becomes of a (gate, up) pair of pre-activations.
+//   kActSilu        silu(g) * u
+//   kActGeluTanh    gelu(g) * u, gelu in its tanh form
+//   kActClampedGlu  g' = min(g, limit), u' = clamp(u, -limit, limit);  g' sigmoid(1.702 g') (u' + 1)
+constexpr int kActSilu = 0, kActGeluTanh = 1, kActClampedGlu = 2;
+__device__ __forceinline__ float act_gelu_tanh(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+__device__ __forceinline__ float gated_act(float g, float u, int act, float limit) {
+    if (act == kActClampedGlu) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return __fdiv_rn(g, 1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return (act == kActGeluTanh ? act_gelu_tanh(g) : act_silu(g)) * u;
+}
+
 template <typename T> __device__ __forceinline__ bool rows_vectorise(const T* base, int n) {
     return (n * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
 }

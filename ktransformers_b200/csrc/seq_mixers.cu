@@ -12,7 +12,9 @@
 //                                  a_t = sigmoid(z_t + b)^(1/tau)
 //   ktb200_gla_out                 per-head RMS norm of o times silu(gate)
 //   ktb200_xielu                   z > 0: sp(p) z^2 + z/2 ;  z <= 0: (1/2 + sp(q)) (exp(z) - 1 - z) + z/2 ,  sp = softplus
-//   ktb200_gated_act_mul           act(gate) * up over rows [gate | up], act = SiLU or the tanh form of GELU
+//   ktb200_gated_act_mul           gated activation of (gate, up) rows: SiLU or tanh-GELU of the gate times up, or the clamped sigmoid form
+//   ktb200_relu_squared            relu(z)^2
+//   ktb200_softcap                 c tanh(z / c) into fp32
 //
 // Storage type T (bf16 or float) for activations, weights and cache rows; every sum, norm, score, weight, decay and state is
 // fp32.  Rows are addressed through per-token / per-sequence index arrays: one launch serves a ragged batch.
@@ -588,17 +590,28 @@ __global__ void xielu_kernel(const T* __restrict__ z, T* __restrict__ out, const
 }
 
 // ------------------------------------------------------------------------------------------------ gated activation
-// out[t][i] = act(gu[t][i]) * gu[t][F + i] for rows [gate F | up F]; act 0: SiLU, 1: the tanh form of GELU
-__device__ __forceinline__ float act_gelu_tanh(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+// out[t][i] = gated_act(gate[t * stride + i], up[t * stride + i]) (seq_common.cuh); rows [gate F | up F]: up = gate + F, stride = 2 F
 template <typename T>
-__global__ void gated_act_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long n_rows, int F, int act) {
+__global__ void gated_act_mul_kernel(const T* __restrict__ gate, const T* __restrict__ up, long stride, T* __restrict__ out, long n_rows, int F, int act, float limit) {
     const long n = n_rows * F;
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
         const long t = i / F;
         const int c = (int)(i - t * F);
-        const float g = to_f(gu[t * 2 * F + c]), u = to_f(gu[t * 2 * F + F + c]);
-        out[i] = from_f<T>((act == 1 ? act_gelu_tanh(g) : act_silu(g)) * u);
+        out[i] = from_f<T>(gated_act(to_f(gate[t * stride + c]), to_f(up[t * stride + c]), act, limit));
     }
+}
+// out = relu(z)^2, element by element
+template <typename T>
+__global__ void relu_squared_kernel(const T* __restrict__ z, T* __restrict__ out, long n) {
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const float r = fmaxf(to_f(z[i]), 0.f);
+        out[i] = from_f<T>(r * r);
+    }
+}
+// out = c tanh(z / c) in fp32, element by element
+template <typename T>
+__global__ void softcap_kernel(const T* __restrict__ z, float* __restrict__ out, long n, float cap) {
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) out[i] = cap * tanhf(to_f(z[i]) / cap);
 }
 
 }  // namespace ktb
@@ -763,10 +776,27 @@ extern "C" int ktb200_xielu(const void* z, void* out, const float* pq, long n, i
     return KTB200_OK;
 }
 
-extern "C" int ktb200_gated_act_mul(const void* gate_up, void* out, int n_tokens, int ff, int act, int dtype, void* stream) {
-    if (!gate_up || !out || ff <= 0 || (act != 0 && act != 1)) { set_error("gated_act_mul: bad argument"); return KTB200_EINVAL; }
+extern "C" int ktb200_gated_act_mul(const void* gate, const void* up, long in_stride, void* out, int n_tokens, int ff, int act, float limit, int dtype, void* stream) {
+    if (!gate || !up || !out || ff <= 0 || in_stride < ff || act < kActSilu || act > kActClampedGlu) { set_error("gated_act_mul: bad argument"); return KTB200_EINVAL; }
     if (n_tokens <= 0) return KTB200_OK;
-    SEQ_DISPATCH(dtype, (gated_act_mul_kernel<T><<<grid_for((long)n_tokens * ff, 256 * 4), 256, 0, (cudaStream_t)stream>>>((const T*)gate_up, (T*)out, n_tokens, ff, act)));
+    SEQ_DISPATCH(dtype, (gated_act_mul_kernel<T><<<grid_for((long)n_tokens * ff, 256 * 4), 256, 0, (cudaStream_t)stream>>>((const T*)gate, (const T*)up, in_stride, (T*)out,
+                                                                                                                         n_tokens, ff, act, limit)));
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+extern "C" int ktb200_relu_squared(const void* z, void* out, long n, int dtype, void* stream) {
+    if (!z || !out) { set_error("relu_squared: bad argument"); return KTB200_EINVAL; }
+    if (n <= 0) return KTB200_OK;
+    SEQ_DISPATCH(dtype, (relu_squared_kernel<T><<<grid_for(n, 256 * 4), 256, 0, (cudaStream_t)stream>>>((const T*)z, (T*)out, n)));
+    KTB_LAUNCH_CHECK();
+    return KTB200_OK;
+}
+
+extern "C" int ktb200_softcap(const void* z, float* out, long n, float cap, int dtype, void* stream) {
+    if (!z || !out || !(cap > 0.f)) { set_error("softcap: bad argument"); return KTB200_EINVAL; }
+    if (n <= 0) return KTB200_OK;
+    SEQ_DISPATCH(dtype, (softcap_kernel<T><<<grid_for(n, 256 * 4), 256, 0, (cudaStream_t)stream>>>((const T*)z, out, n, cap)));
     KTB_LAUNCH_CHECK();
     return KTB200_OK;
 }

@@ -1,14 +1,15 @@
 // Token-major operators of decoder layers that keep a 32-bit residual stream and per-sequence state (libktb200_seq.so).
 //
-//   ktb200_group_rmsnorm_shift   x_out = x_in + mult * (a + b)   (optional), then RMS norm in `groups` equal parts, then an
+//   ktb200_group_rmsnorm_shift   x_out = x_in + mult * (a + b) + row   (each optional; row: one vector for all tokens), then RMS norm in `groups` equal parts, then an
 //                                optional token shift  hs_t = h_t + (h_{t-1} - h_t) * mu  whose h_{t-1} comes from the same
 //                                step (recomputed from the previous row) or from the per-sequence state rows
 //   ktb200_latent_prep           what follows the fused down-projections of latent attention: RMS norm of the query latent,
 //                                RMS norm of the key/value latent, rotation of the shared rotated key part, paged cache write
 //   ktb200_sigmoid_gate_mul      heads [H][T][dv] * sigmoid(gate [T][H*dv]) -> [T][H*dv]
 //   ktb200_poly_norm             a N(z) + b N(z^2) + c N(z^3) + e,  N(y) = y / sqrt(mean(y^2) + eps) over a token's row
-//   ktb200_experts_gate_up/_down per (token, slot) pair GEMVs over dense (bf16 / f32) expert weights: silu(gate) * up, then
-//                                the weighted sum of the chosen experts' down projections in fp32
+//   ktb200_experts_gate_up/_down per (token, slot) pair GEMVs over dense (bf16 / f32) expert weights: a gated activation of (gate, up)
+//                                (seq_common.cuh: SiLU, tanh-GELU or the clamped sigmoid form), then the weighted sum of the chosen
+//                                experts' down projections in fp32
 //
 // Every kernel is templated on the storage type T (bf16 or float) of activations and weights; norms, angles, the residual
 // sum, sigmoid / silu arguments and all reductions are fp32 (angles: fp64 tables).  Rows are addressed through per-token
@@ -27,7 +28,7 @@ namespace ktb {
 constexpr int kNormBatch = 4;
 template <typename T>
 __global__ void __launch_bounds__(256) group_norm_shift_kernel(const float* __restrict__ x_in, const void* da, int a_type, const void* db, int b_type, float mult,
-                                                               float* __restrict__ x_out, const T* __restrict__ w, int groups, float eps, const T* __restrict__ mu,
+                                                               const float* __restrict__ row_add, float* __restrict__ x_out, const T* __restrict__ w, int groups, float eps, const T* __restrict__ mu,
                                                                const int* __restrict__ prev_idx, const int* __restrict__ rd_row, const int* __restrict__ wr_row,
                                                                float* __restrict__ state, T* __restrict__ h_out, T* __restrict__ hs_out, int D, int stash, int vec) {
     extern __shared__ __align__(16) float sm[];
@@ -37,7 +38,7 @@ __global__ void __launch_bounds__(256) group_norm_shift_kernel(const float* __re
     float* prv = cur + D;
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
     const int gs = D / groups;
-    const bool add = da != nullptr || db != nullptr;
+    const bool add = da != nullptr || db != nullptr || row_add != nullptr;
     const int pi = (mu && prev_idx) ? prev_idx[t] : -1;      // row of the previous token inside this step, or -1
     const int rr = (mu && rd_row) ? rd_row[t] : -1;
     const int wr = (mu && wr_row) ? wr_row[t] : -1;
@@ -48,6 +49,7 @@ __global__ void __launch_bounds__(256) group_norm_shift_kernel(const float* __re
             if (da) s += load_hidden(da, (long)r * D + i, a_type);
             if (db) s += load_hidden(db, (long)r * D + i, b_type);
             v = v + mult * s;
+            if (row_add) v += row_add[i];
         }
         return v;
     };
@@ -58,6 +60,7 @@ __global__ void __launch_bounds__(256) group_norm_shift_kernel(const float* __re
             if (da) { const float4 u = load4_hidden(da, (long)r * D + i, a_type); s.x += u.x; s.y += u.y; s.z += u.z; s.w += u.w; }
             if (db) { const float4 u = load4_hidden(db, (long)r * D + i, b_type); s.x += u.x; s.y += u.y; s.z += u.z; s.w += u.w; }
             v.x = v.x + mult * s.x; v.y = v.y + mult * s.y; v.z = v.z + mult * s.z; v.w = v.w + mult * s.w;
+            if (row_add) { const float4 u = load4(row_add + i); v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w; }
         }
         return v;
     };
@@ -269,12 +272,12 @@ __global__ void __launch_bounds__(256) poly_norm_kernel(const T* __restrict__ z,
 }
 
 // ------------------------------------------------------------------------------------------------ dense experts, per pair
-// Two kinds of expert: gated (silu(W_gate x) * W_up x) and, with no gate matrix (Wg == nullptr), relu(W_up x)^2.
+// Two kinds of expert: gated (gated_act(W_gate x, W_up x), seq_common.cuh) and, with no gate matrix (Wg == nullptr), relu(W_up x)^2.
 __device__ __forceinline__ float act_relu_sq(float x) { const float r = fmaxf(x, 0.f); return r * r; }
 // grid (pairs, row blocks); a warp owns ff rows r = blockIdx.y * nw + warp (+ stride); the token's row sits in shared memory.
 template <typename T>
 __global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restrict__ x, const int64_t* __restrict__ ids, int top, const T* __restrict__ Wg, const T* __restrict__ Wu,
-                                                              T* __restrict__ act, int D, int F) {
+                                                              T* __restrict__ act, int D, int F, int act_kind, float limit) {
     extern __shared__ __align__(16) float xs[];
     const long p = blockIdx.x;
     const long t = p / top;
@@ -298,7 +301,7 @@ __global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restric
         float su = lane_dot(u + (long)r * D, xs, D, lane, vec);
         sg = warp_sum(sg);
         su = warp_sum(su);
-        if (lane == 0) act[p * F + r] = from_f<T>(act_silu(sg) * su);
+        if (lane == 0) act[p * F + r] = from_f<T>(gated_act(sg, su, act_kind, limit));
     }
 }
 
@@ -449,7 +452,7 @@ __device__ __forceinline__ void lane_dot_rows(const float* const (&w)[NW], const
 // shared memory: list[P + 1] ints (padded to 16 bytes) | rows [NT][D] of T.  A warp takes two ff rows at a time (gate and up of each).
 template <typename T, int NT>
 __global__ void __launch_bounds__(256) experts_gate_up_by_expert_kernel(const T* __restrict__ x, const int64_t* __restrict__ ids, int top, int P, const T* __restrict__ Wg,
-                                                                        const T* __restrict__ Wu, T* __restrict__ act, int D, int F) {
+                                                                        const T* __restrict__ Wu, T* __restrict__ act, int D, int F, int act_kind, float limit) {
     extern __shared__ __align__(16) unsigned char sm_raw[];
     int* list = reinterpret_cast<int*>(sm_raw);
     T* xs = reinterpret_cast<T*>(sm_raw + (((size_t)(P + 1) * sizeof(int) + 15) & ~(size_t)15));
@@ -501,8 +504,8 @@ __global__ void __launch_bounds__(256) experts_gate_up_by_expert_kernel(const T*
                     const float a0 = warp_sum(s[0][k]), b0 = warp_sum(s[1][k]), a1 = warp_sum(s[2][k]), b1 = warp_sum(s[3][k]);
                     if (lane == 0) {
                         T* o = act + (long)list[c + k] * F;
-                        o[r] = from_f<T>(act_silu(a0) * b0);
-                        if (r1 != r) o[r1] = from_f<T>(act_silu(a1) * b1);
+                        o[r] = from_f<T>(gated_act(a0, b0, act_kind, limit));
+                        if (r1 != r) o[r1] = from_f<T>(gated_act(a1, b1, act_kind, limit));
                     }
                 }
             }
@@ -574,23 +577,23 @@ using namespace ktb;
         else { set_error("dtype must be bf16 or f32"); return KTB200_EINVAL; }             \
     } while (0)
 
-extern "C" int ktb200_group_rmsnorm_shift(const float* x_in, const void* delta_a, int a_type, const void* delta_b, int b_type, float mult, float* x_out,
+extern "C" int ktb200_group_rmsnorm_shift(const float* x_in, const void* delta_a, int a_type, const void* delta_b, int b_type, float mult, const float* row_add, float* x_out,
                                           const void* weight, int groups, float eps, const void* shift, const int* prev_idx, const int* rd_row, const int* wr_row,
                                           float* state, void* h_out, void* hs_out, int n_tokens, int width, int dtype, void* stream) {
     if (!x_in || !weight || groups <= 0 || width <= 0 || width % groups || n_tokens < 0) { set_error("group_rmsnorm_shift: bad argument"); return KTB200_EINVAL; }
-    if ((delta_a || delta_b) && (!x_out || x_out == x_in)) { set_error("group_rmsnorm_shift: the sum needs a separate output row buffer"); return KTB200_EINVAL; }
+    if ((delta_a || delta_b || row_add) && (!x_out || x_out == x_in)) { set_error("group_rmsnorm_shift: the sum needs a separate output row buffer"); return KTB200_EINVAL; }
     if (shift && (!prev_idx || !rd_row || !wr_row || !state || !hs_out)) { set_error("group_rmsnorm_shift: shift needs its index rows, state and output"); return KTB200_EINVAL; }
     if (n_tokens == 0) return KTB200_OK;
     size_t smem = (size_t)((2 * groups + 3) & ~3) * sizeof(float);
     const int stash = smem + (2 * (size_t)width + 64) * sizeof(float) <= 160 * 1024;
     if (stash) smem += (2 * (size_t)width + 64) * sizeof(float);      // two staged rows + the warps' partial sums
     auto al = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
-    const int vec = width % 4 == 0 && (width / groups) % 4 == 0 && al(x_in, 16) && al(x_out, 16) && al(delta_a, 16) && al(delta_b, 16) && al(weight, 16) && al(shift, 16) &&
+    const int vec = width % 4 == 0 && (width / groups) % 4 == 0 && al(x_in, 16) && al(x_out, 16) && al(delta_a, 16) && al(delta_b, 16) && al(row_add, 16) && al(weight, 16) && al(shift, 16) &&
                     al(state, 16) && al(h_out, 16) && al(hs_out, 16);
     SEQ_DISPATCH(dtype, {
         static size_t granted = 48 * 1024;      // opt-in shared memory, raised once per size
         if (smem > granted) { KTB_CUDA_CHECK(cudaFuncSetAttribute(group_norm_shift_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); granted = smem; }
-        group_norm_shift_kernel<T><<<n_tokens, 256, smem, (cudaStream_t)stream>>>(x_in, delta_a, a_type, delta_b, b_type, mult, x_out, (const T*)weight, groups, eps,
+        group_norm_shift_kernel<T><<<n_tokens, 256, smem, (cudaStream_t)stream>>>(x_in, delta_a, a_type, delta_b, b_type, mult, row_add, x_out, (const T*)weight, groups, eps,
                                                                                   (const T*)shift, prev_idx, rd_row, wr_row, state, (T*)h_out, (T*)hs_out, width, stash, vec);
     });
     KTB_LAUNCH_CHECK();
@@ -646,9 +649,9 @@ extern "C" int ktb200_poly_norm(const void* z, void* out, const float* coef, flo
     return KTB200_OK;
 }
 
-extern "C" int ktb200_experts_gate_up(const void* x, const int64_t* ids, int top, const void* w_gate, const void* w_up, void* act, int n_tokens, int width, int ff, int dtype,
-                                      void* stream) {
-    if (!x || !ids || !w_up || !act || top <= 0 || width <= 0 || ff <= 0 || width * sizeof(float) > 200 * 1024) { set_error("experts_gate_up: bad argument"); return KTB200_EINVAL; }
+extern "C" int ktb200_experts_gate_up(const void* x, const int64_t* ids, int top, const void* w_gate, const void* w_up, void* act, int n_tokens, int width, int ff, int act_kind,
+                                      float limit, int dtype, void* stream) {
+    if (!x || !ids || !w_up || !act || top <= 0 || width <= 0 || ff <= 0 || width * sizeof(float) > 200 * 1024 || act_kind < kActSilu || act_kind > kActClampedGlu) { set_error("experts_gate_up: bad argument"); return KTB200_EINVAL; }
     if (n_tokens <= 0) return KTB200_OK;
     const size_t smem = (size_t)width * sizeof(float);
     int ry = (ff + 7) / 8;   // row blocks: enough CTAs to fill 148 SMs several times over when there are few pairs
@@ -656,7 +659,7 @@ extern "C" int ktb200_experts_gate_up(const void* x, const int64_t* ids, int top
     SEQ_DISPATCH(dtype, {
         static size_t granted = 48 * 1024;
         if (smem > granted) { KTB_CUDA_CHECK(cudaFuncSetAttribute(experts_gate_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); granted = smem; }
-        experts_gate_up_kernel<T><<<dim3(n_tokens * top, ry), 256, smem, (cudaStream_t)stream>>>((const T*)x, ids, top, (const T*)w_gate, (const T*)w_up, (T*)act, width, ff);
+        experts_gate_up_kernel<T><<<dim3(n_tokens * top, ry), 256, smem, (cudaStream_t)stream>>>((const T*)x, ids, top, (const T*)w_gate, (const T*)w_up, (T*)act, width, ff, act_kind, limit);
     });
     KTB_LAUNCH_CHECK();
     return KTB200_OK;
@@ -699,16 +702,16 @@ static int by_expert_staged(int staged, int pairs, int n_experts) { return stage
     })
 
 extern "C" int ktb200_experts_gate_up_by_expert(const void* x, const int64_t* ids, int top, int n_experts, const void* w_gate, const void* w_up, void* act, int n_tokens, int width,
-                                                int ff, int staged, int dtype, void* stream) {
-    if (!x || !ids || !w_up || !act || top <= 0 || n_experts <= 0 || width <= 0 || ff <= 0) { set_error("experts_gate_up_by_expert: bad argument"); return KTB200_EINVAL; }
+                                                int ff, int staged, int act_kind, float limit, int dtype, void* stream) {
+    if (!x || !ids || !w_up || !act || top <= 0 || n_experts <= 0 || width <= 0 || ff <= 0 || act_kind < kActSilu || act_kind > kActClampedGlu) { set_error("experts_gate_up_by_expert: bad argument"); return KTB200_EINVAL; }
     if (n_tokens <= 0) return KTB200_OK;
     const int P = n_tokens * top;
     if (by_expert_staged(staged, P, n_experts) == 4) {
         constexpr int NT = 4;
-        BY_EXPERT_LAUNCH(experts_gate_up_by_expert_kernel, ff, 2, (size_t)width, (const T*)x, ids, top, P, (const T*)w_gate, (const T*)w_up, (T*)act, width, ff);
+        BY_EXPERT_LAUNCH(experts_gate_up_by_expert_kernel, ff, 2, (size_t)width, (const T*)x, ids, top, P, (const T*)w_gate, (const T*)w_up, (T*)act, width, ff, act_kind, limit);
     } else {
         constexpr int NT = 2;
-        BY_EXPERT_LAUNCH(experts_gate_up_by_expert_kernel, ff, 2, (size_t)width, (const T*)x, ids, top, P, (const T*)w_gate, (const T*)w_up, (T*)act, width, ff);
+        BY_EXPERT_LAUNCH(experts_gate_up_by_expert_kernel, ff, 2, (size_t)width, (const T*)x, ids, top, P, (const T*)w_gate, (const T*)w_up, (T*)act, width, ff, act_kind, limit);
     }
     KTB_LAUNCH_CHECK();
     return KTB200_OK;

@@ -1,13 +1,16 @@
-// Soft-max attention over grouped key/value heads in a paged cache, with a partial rotation, unit-rms queries and keys, capped
-// scores, a sliding window and values blended with another layer's (libktb200_seq.so).
+// Soft-max attention over grouped key/value heads in a paged cache, with a partial rotation, normed queries and keys, capped
+// scores, a sliding-window or chunked mask and values blended with another layer's (libktb200_seq.so).
 //
 //   ktb200_rope_norm_cache_write   proj rows [... q H*d ... k G*d ... v G*dv ...]: q and k turn over their first rot_dims columns (pairs of
-//                                  either layout, angle pos * inv_freq[i]), are scaled to unit rms head by head (optional),
-//                                  v <- (1 - t) v + t v_other with one learned t (optional); [k | v] into the paged cache, q into q_out
-//   ktb200_window_softmax_attn     o_i = sum_j softmax_j(cap(scale q_i.k_j)) v_j over the keys j with 0 <= i - j < window (window <= 0: all
-//                                  j <= i), cap(s) = c tanh(s / c), c = softcap (softcap <= 0: none); query head h reads key/value
-//                                  head h / (H / G); the key range is cut into splits for few tokens on long ranges; bf16 with head
-//                                  sizes that are multiples of 16 up to 128: m16n8k16 tensor-core tiles
+//                                  either layout, angle pos * inv_freq[i]), then (qk_norm 1) are scaled to unit rms head by head, or
+//                                  (qk_norm 2) divided by the rms of the WHOLE q (k) row and multiplied by a weight per column;
+//                                  v <- (1 - t) v + t v_other with one learned t (optional), then each value head to unit rms (optional);
+//                                  [k | v] into the paged cache, q into q_out
+//   ktb200_window_softmax_attn     o_i = sum_j softmax_j(cap(scale t_h q_i.k_j)) v_j over the keys j <= i with i - j < window (window > 0)
+//                                  and floor(j / chunk) == floor(i / chunk) (chunk > 0), cap(s) = c tanh(s / c), c = softcap (softcap <= 0:
+//                                  none), t_h one learned number per query head (optional); query head h reads key/value head h / (H / G); the
+//                                  key range is cut into splits for few tokens on long ranges; bf16 with head sizes that are multiples of 16
+//                                  up to 128: m16n8k16 tensor-core tiles
 //
 // Storage type T (bf16 or float) for activations and cache rows; rotation, norms, scores, the cap and the soft-max are fp32
 // (angles fp64).  Cache row of a token: [k G*d | v G*dv]; a sequence's page table row is a ring.
@@ -23,13 +26,15 @@ namespace ktb {
 // One CTA per token, a warp per head (query heads first, then key heads).  The token's rot_dims / 2 angles are turned into
 // (cos, sin) once per CTA (fp64 angle and sincos, kept as fp32) and shared by all heads.
 constexpr int kPrepMaxPerLane = 8;      // head size <= 256
+constexpr int kQkNormNone = 0, kQkNormHead = 1, kQkNormRow = 2;
 template <typename T>
 __global__ void __launch_bounds__(256) rope_norm_cache_write_kernel(const T* __restrict__ proj, long proj_stride, int q_off, int k_off, int v_off, int H, int G, int d, int dv,
-                                                                    int rot_dims, int rot_layout, const double* __restrict__ inv_freq, int unit_rms, float eps,
-                                                                    const T* __restrict__ v_other, long v_other_stride, const float* __restrict__ blend,
+                                                                    int rot_dims, int rot_layout, const double* __restrict__ inv_freq, int qk_norm, const T* __restrict__ q_w,
+                                                                    const T* __restrict__ k_w, int v_unit_rms, float eps, const T* __restrict__ v_other, long v_other_stride, const float* __restrict__ blend,
                                                                     const int* __restrict__ pos, const int* __restrict__ slot, const int* __restrict__ page_table,
                                                                     int max_pages, int page_size, T* __restrict__ cache, T* __restrict__ q_out) {
     __shared__ float2 turn[16 * kPrepMaxPerLane];      // (cos, sin) of the token's angles
+    __shared__ float red[8], row_inv[2];
     const long t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int p = pos[t], half = rot_dims >> 1;
@@ -40,6 +45,18 @@ __global__ void __launch_bounds__(256) rope_norm_cache_write_kernel(const T* __r
     }
     __syncthreads();
     const T* row = proj + t * proj_stride;
+    if (qk_norm == kQkNormRow) {      // a turn keeps x^2 + y^2 of its pair: the row's mean square is that of the un-turned columns
+        float sq = 0.f, sk = 0.f;
+        for (int i = threadIdx.x; i < H * d; i += blockDim.x) { const float v = to_f(row[q_off + i]); sq += v * v; }
+        for (int i = threadIdx.x; i < G * d; i += blockDim.x) { const float v = to_f(row[k_off + i]); sk += v * v; }
+        sq = block_sum(sq, red);
+        sk = block_sum(sk, red);
+        if (threadIdx.x == 0) {
+            row_inv[0] = 1.0f / sqrtf(sq / (float)(H * d) + eps);
+            row_inv[1] = 1.0f / sqrtf(sk / (float)(G * d) + eps);
+        }
+        __syncthreads();
+    }
     const long crow = ((long)page_table[(long)slot[t] * max_pages + (p / page_size) % max_pages] * page_size + p % page_size) * ((long)G * (d + dv));
     for (int hh = warp; hh < H + G; hh += nw) {
         const bool is_q = hh < H;
@@ -63,19 +80,39 @@ __global__ void __launch_bounds__(256) rope_norm_cache_write_kernel(const T* __r
             }
         }
         float inv = 1.f;
-        if (unit_rms) {
+        if (qk_norm == kQkNormHead) {
             s = warp_sum(s);
             inv = 1.0f / sqrtf(s / (float)d + eps);
+        } else if (qk_norm == kQkNormRow) {
+            inv = row_inv[is_q ? 0 : 1];
         }
         T* dst = is_q ? q_out + (t * H + hh) * d : cache + crow + (long)(hh - H) * d;
+        const T* wrow = qk_norm == kQkNormRow ? (is_q ? q_w + (long)hh * d : k_w + (long)(hh - H) * d) : nullptr;
 #pragma unroll
         for (int e = 0; e < kPrepMaxPerLane; e++) {
             const int i = lane + 32 * e;
-            if (i < d) dst[i] = from_f<T>(r[e] * inv);
+            if (i < d) dst[i] = from_f<T>(wrow ? r[e] * inv * to_f(wrow[i]) : r[e] * inv);
         }
     }
     const T* v = row + v_off;
     const float lam = v_other ? blend[0] : 0.f;
+    if (v_unit_rms) {      // a warp per value head: mean square over the head's columns, then the scaled columns
+        for (int g = warp; g < G; g += nw) {
+            float s = 0.f;
+            for (int i = lane; i < dv; i += 32) {
+                float x = to_f(v[g * dv + i]);
+                if (v_other) x = (1.0f - lam) * x + lam * to_f(v_other[t * v_other_stride + g * dv + i]);
+                s += x * x;
+            }
+            const float inv = 1.0f / sqrtf(warp_sum(s) / (float)dv + eps);
+            for (int i = lane; i < dv; i += 32) {
+                float x = to_f(v[g * dv + i]);
+                if (v_other) x = (1.0f - lam) * x + lam * to_f(v_other[t * v_other_stride + g * dv + i]);
+                cache[crow + (long)G * d + g * dv + i] = from_f<T>(x * inv);
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
         float x = to_f(v[i]);
         if (v_other) x = (1.0f - lam) * x + lam * to_f(v_other[t * v_other_stride + i]);
@@ -90,10 +127,16 @@ __global__ void __launch_bounds__(256) rope_norm_cache_write_kernel(const T* __r
 constexpr int kSmTile = 32;
 constexpr int kSmMaxCols = 8;      // value columns per lane: vdim <= 256
 __device__ __forceinline__ float cap_score(float s, float softcap) { return softcap > 0.f ? softcap * tanhf(s / softcap) : s; }
+// the first key that the query at position p sees: the start of its window, or of its chunk (chunks are counted from position 0)
+__device__ __forceinline__ int first_visible(int p, int window, int chunk) {
+    int lo = window > 0 ? max(0, p - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, p - p % chunk);
+    return lo;
+}
 
 template <typename T>
-__global__ void __launch_bounds__(256) window_softmax_attn_kernel(const T* __restrict__ q, int H, int G, int d, int dv, float scale, float softcap, int window,
-                                                                  const int* __restrict__ pos, const int* __restrict__ slot, const int* __restrict__ page_table,
+__global__ void __launch_bounds__(256) window_softmax_attn_kernel(const T* __restrict__ q, int H, int G, int d, int dv, float scale, const float* __restrict__ head_scale,
+                                                                  float softcap, int window, int chunk, const int* __restrict__ pos, const int* __restrict__ slot, const int* __restrict__ page_table,
                                                                   int max_pages, int page_size, const T* __restrict__ cache, T* __restrict__ out,
                                                                   float* __restrict__ partial, int n_tokens) {
     extern __shared__ __align__(16) float sm[];
@@ -109,7 +152,7 @@ __global__ void __launch_bounds__(256) window_softmax_attn_kernel(const T* __res
     float* pw = Vs + kSmTile * dv;
     const int p = pos[t];
     // this split's part of the visible range [lo, p], in whole tiles counted from lo
-    const int lo = window > 0 ? max(0, p - window + 1) : 0, n_keys = p + 1 - lo;
+    const int lo = first_visible(p, window, chunk), n_keys = p + 1 - lo;
     const int splits = gridDim.z;
     const int per = ((n_keys + splits - 1) / splits + kSmTile - 1) / kSmTile * kSmTile;
     const int k_lo = lo + blockIdx.z * per, k_hi = min(p + 1, k_lo + per);
@@ -118,8 +161,10 @@ __global__ void __launch_bounds__(256) window_softmax_attn_kernel(const T* __res
     for (int c = 0; c < kSmMaxCols; c++) acc[c] = 0.f;
     float m = -INFINITY, l = 0.f;
     if (k_lo < k_hi) {
-        if (live)
-            for (int i = lane; i < d; i += 32) qs[warp * d + i] = to_f(q[(t * H + h) * d + i]) * scale;
+        if (live) {
+            const float sc = head_scale ? scale * head_scale[h] : scale;
+            for (int i = lane; i < d; i += 32) qs[warp * d + i] = to_f(q[(t * H + h) * d + i]) * sc;
+        }
         const int* pt = page_table + (long)slot[t] * max_pages;
         const long cw = (long)G * (d + dv);
         for (int j0 = k_lo; j0 < k_hi; j0 += kSmTile) {
@@ -193,8 +238,8 @@ __device__ __forceinline__ float cap_score_fast(float s, float two_over_cap, flo
 
 template <int D16MAX, int DV16MAX>
 __global__ void __launch_bounds__(kMmaRows * 2, 4) window_softmax_attn_mma_kernel(
-    const __nv_bfloat16* __restrict__ q, int H, int G, int d, int dv, float scale, float softcap, int window, const int* __restrict__ pos, const int* __restrict__ slot,
-    const int* __restrict__ seqs, int seqs_stride, int n_seqs, int RH, const int* __restrict__ page_table, int max_pages, int page_size, const __nv_bfloat16* __restrict__ cache,
+    const __nv_bfloat16* __restrict__ q, int H, int G, int d, int dv, float scale, const float* __restrict__ head_scale, float softcap, int window, int chunk,
+    const int* __restrict__ pos, const int* __restrict__ slot, const int* __restrict__ seqs, int seqs_stride, int n_seqs, int RH, const int* __restrict__ page_table, int max_pages, int page_size, const __nv_bfloat16* __restrict__ cache,
     __nv_bfloat16* __restrict__ out, float* __restrict__ partial) {
     constexpr int ROWS = kMmaRows, KEYS = kMmaKeys;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -224,7 +269,7 @@ __global__ void __launch_bounds__(kMmaRows * 2, 4) window_softmax_attn_mma_kerne
     __nv_bfloat16* Vs = Ks + 2 * KEYS * ldk;                 // [2][KEYS][ldv]
     const int pos0 = pos[tok0], max_pos = pos0 + ntok - 1;
     // the tile's key range [lo, max_pos], cut into this split's part in whole key tiles counted from lo
-    const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int lo = first_visible(pos0, window, chunk);
     const int splits = gridDim.z, n_keys = max_pos + 1 - lo;
     const int per = ((n_keys + splits - 1) / splits + KEYS - 1) / KEYS * KEYS;
     const int k_lo = lo + blockIdx.z * per, k_hi = min(max_pos + 1, k_lo + per);
@@ -233,9 +278,12 @@ __global__ void __launch_bounds__(kMmaRows * 2, 4) window_softmax_attn_mma_kerne
     const int tokA = rA / RH, tokB = rB / RH, hA = h0 + rA % RH, hB = h0 + rB % RH;
     const bool vA = tokA < ntok, vB = tokB < ntok;
     const int pA = pos0 + tokA, pB = pos0 + tokB;
+    const int fA = first_visible(pA, window, chunk), fB = first_visible(pB, window, chunk);
+    const float scA = head_scale ? scale * head_scale[hA] : scale, scB = head_scale ? scale * head_scale[hB] : scale;
     const bool warp_live = (warp * 16) / RH < ntok;
     const int warp_max_pos = pos0 + min(ntok - 1, (warp * 16 + 15) / RH), warp_min_pos = pos0 + (warp * 16) / RH;
-    const int warp_first_key = window > 0 ? warp_min_pos - window + 1 : 0;      // no row of this warp sees a key before this one
+    const int warp_first_key = first_visible(warp_min_pos, window, chunk);      // no row of this warp sees a key before this one
+    const int warp_last_first = first_visible(warp_max_pos, window, chunk);    // every row of this warp sees the keys from here to its own
     const float two_over_cap = softcap > 0.f ? 2.0f / softcap : 0.f;
     float O[2 * DV16MAX][4];
 #pragma unroll
@@ -300,20 +348,19 @@ __global__ void __launch_bounds__(kMmaRows * 2, 4) window_softmax_attn_mma_kerne
                 }
             }
             // nothing to mask: all 16 rows carry tokens, and every key of the tile lies at or before the earliest of them, inside the
-            // window of the latest and inside this split
-            const bool plain = (warp * 16 + 15) / RH < ntok && j0 + KEYS - 1 <= warp_min_pos && (window <= 0 || j0 > warp_max_pos - window) && j0 + KEYS <= k_hi;
+            // window or chunk of the latest and inside this split
+            const bool plain = (warp * 16 + 15) / RH < ntok && j0 + KEYS - 1 <= warp_min_pos && j0 >= warp_last_first && j0 + KEYS <= k_hi;
             float tmA = -INFINITY, tmB = -INFINITY;
 #pragma unroll
             for (int n = 0; n < KEYS / 8; n++) {
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    float s = S[n][e] * scale;
+                    float s = S[n][e] * (e < 2 ? scA : scB);
                     if (softcap > 0.f) s = cap_score_fast(s, two_over_cap, softcap);
                     if (!plain) {
                         const int key = j0 + n * 8 + 2 * tq + (e & 1);
                         const bool second = e >= 2;
-                        const int dist = (second ? pB : pA) - key;
-                        const bool ok = (second ? vB : vA) && dist >= 0 && (window <= 0 || dist < window) && key < k_hi;
+                        const bool ok = (second ? vB : vA) && key <= (second ? pB : pA) && key >= (second ? fB : fA) && key < k_hi;
                         if (!ok) s = -INFINITY;
                     }
                     S[n][e] = s;
@@ -446,19 +493,19 @@ using namespace ktb;
     } while (0)
 
 extern "C" int ktb200_rope_norm_cache_write(const void* proj, long proj_stride, int q_off, int k_off, int v_off, int heads, int kv_heads, int dim, int vdim, int rot_dims,
-                                            int rot_layout, const double* inv_freq, int unit_rms, float eps, const void* v_other, long v_other_stride, const float* blend,
-                                            const int* pos, const int* slot, const int* page_table, int max_pages, int page_size, void* cache, void* q_out, int n_tokens,
+                                            int rot_layout, const double* inv_freq, int qk_norm, const void* q_weight, const void* k_weight, int v_unit_rms, float eps,
+                                            const void* v_other, long v_other_stride, const float* blend, const int* pos, const int* slot, const int* page_table, int max_pages, int page_size, void* cache, void* q_out, int n_tokens,
                                             int dtype, void* stream) {
     if (!proj || !pos || !slot || !page_table || !cache || !q_out || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || dim > 32 * kPrepMaxPerLane || vdim <= 0 ||
         rot_dims < 0 || rot_dims > dim || (rot_dims & 1) || (rot_dims && !inv_freq) || (rot_layout != kRotInterleaved && rot_layout != kRotHalves) || (v_other && !blend) ||
-        page_size <= 0 || max_pages <= 0) {
+        qk_norm < kQkNormNone || qk_norm > kQkNormRow || (qk_norm == kQkNormRow && (!q_weight || !k_weight)) || page_size <= 0 || max_pages <= 0) {
         set_error("rope_norm_cache_write: bad argument (head size <= %d)", 32 * kPrepMaxPerLane);
         return KTB200_EINVAL;
     }
     if (n_tokens <= 0) return KTB200_OK;
     SEQ_DISPATCH(dtype, (rope_norm_cache_write_kernel<T><<<n_tokens, 256, 0, (cudaStream_t)stream>>>(
-                            (const T*)proj, proj_stride, q_off, k_off, v_off, heads, kv_heads, dim, vdim, rot_dims, rot_layout, inv_freq, unit_rms, eps, (const T*)v_other,
-                            v_other_stride, blend, pos, slot, page_table, max_pages, page_size, (T*)cache, (T*)q_out)));
+                            (const T*)proj, proj_stride, q_off, k_off, v_off, heads, kv_heads, dim, vdim, rot_dims, rot_layout, inv_freq, qk_norm, (const T*)q_weight, (const T*)k_weight, v_unit_rms, eps,
+                            (const T*)v_other, v_other_stride, blend, pos, slot, page_table, max_pages, page_size, (T*)cache, (T*)q_out)));
     KTB_LAUNCH_CHECK();
     return KTB200_OK;
 }
@@ -476,7 +523,8 @@ extern "C" int ktb200_window_softmax_attn_tiles(int heads, int kv_heads, int n_t
     return n_seqs + n_tokens / (kMmaRows / mma_heads_per_tile(heads / kv_heads));
 }
 
-extern "C" int ktb200_window_softmax_attn(const void* q, int heads, int kv_heads, int dim, int vdim, float scale, float softcap, int window, const int* pos, const int* slot,
+extern "C" int ktb200_window_softmax_attn(const void* q, int heads, int kv_heads, int dim, int vdim, float scale, const float* head_scale, float softcap, int window, int chunk,
+                                          const int* pos, const int* slot,
                                           const int* seqs, int seqs_stride, int n_seqs, const int* page_table, int max_pages, int page_size, const void* cache, void* out,
                                           int n_tokens, int splits, float* workspace, int dtype, int allow_tensor_cores, void* stream) {
     if (!q || !pos || !slot || !page_table || !cache || !out || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0 || vdim > 32 * kSmMaxCols ||
@@ -495,7 +543,7 @@ extern "C" int ktb200_window_softmax_attn(const void* q, int heads, int kv_heads
 #define MMA_LAUNCH(DK, DV)                                                                                                                                      \
     do {                                                                                                                                                        \
         GRANT_SMEM((window_softmax_attn_mma_kernel<DK, DV>), smem);                                                                                             \
-        window_softmax_attn_mma_kernel<DK, DV><<<grid, kMmaRows * 2, smem, (cudaStream_t)stream>>>((const B*)q, heads, kv_heads, dim, vdim, scale, softcap, window, pos, slot, \
+        window_softmax_attn_mma_kernel<DK, DV><<<grid, kMmaRows * 2, smem, (cudaStream_t)stream>>>((const B*)q, heads, kv_heads, dim, vdim, scale, head_scale, softcap, window, chunk, pos, slot, \
                                                                                                    seqs, seqs_stride, n_seqs, RH, page_table, max_pages, page_size,  \
                                                                                                    (const B*)cache, (B*)out, splits > 1 ? workspace : nullptr);   \
     } while (0)
@@ -515,7 +563,7 @@ extern "C" int ktb200_window_softmax_attn(const void* q, int heads, int kv_heads
     SEQ_DISPATCH(dtype, {
         GRANT_SMEM(window_softmax_attn_kernel<T>, smem);
         window_softmax_attn_kernel<T><<<dim3(n_tokens, kv_heads * hblocks, splits), HB * 32, smem, (cudaStream_t)stream>>>(
-            (const T*)q, heads, kv_heads, dim, vdim, scale, softcap, window, pos, slot, page_table, max_pages, page_size, (const T*)cache, (T*)out,
+            (const T*)q, heads, kv_heads, dim, vdim, scale, head_scale, softcap, window, chunk, pos, slot, page_table, max_pages, page_size, (const T*)cache, (T*)out,
             splits > 1 ? workspace : nullptr, n_tokens);
         KTB_LAUNCH_CHECK();
         if (splits > 1) {

@@ -10,6 +10,7 @@ MODEL_REGISTRY = {
     "Lekapel": ("ktransformers_b200.models.modeling_lekapel", "LekapelForCausalLM"),
     "Mabidra": ("ktransformers_b200.models.modeling_mabidra", "MabidraForCausalLM"),
     "Zivulix": ("ktransformers_b200.models.modeling_zivulix", "ZivulixForCausalLM"),
+    "Bilurax": ("ktransformers_b200.models.modeling_bilurax", "BiluraxForCausalLM"),
     "DeepseekV3ForCausalLM": ("ktransformers_b200.models.modeling_deepseek_v3", "DeepseekV3MoEOnlyForCausalLM"),
     "DeepseekV2ForCausalLM": ("ktransformers_b200.models.modeling_deepseek", "DeepseekV2MoE"),
 }

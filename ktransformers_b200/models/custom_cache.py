@@ -99,8 +99,8 @@ class PagedStateCache:
       layers share the page ids, so a sequence has ONE page table row (`page_table[slot]`, device int32), used as a ring:
       logical page p sits in column `p % max_pages_per_seq`.
     * A sequence occupies a slot from `open()` to `close()`; `extend(slot, n)` reserves pages for the next n tokens and returns
-      the first position; pages that fall wholly behind `window` (the largest look-back of any layer) are given back while the
-      sequence is still running, and pages and slots are reused without being cleared: readers never look outside
+      the first position; pages that fall wholly behind `window` (the largest look-back of any layer), or before the start of
+      the current chunk when every layer's mask is chunked, are given back while the sequence is still running, and pages and slots are reused without being cleared: readers never look outside
       `[pos - window + 1, pos]`, and position 0 reads no state.
     * State rows are double-buffered per slot (`state[l]` is `[2 * max_slots, width]` fp32): a step reads row `2*slot + parity`
       and writes row `2*slot + 1 - parity`, then `commit()` flips the parity of the slots it touched, so no kernel launch
@@ -110,11 +110,14 @@ class PagedStateCache:
     batch row; this manager adds allocation, release and the recurrent rows."""
 
     def __init__(self, row_widths, state_width, max_tokens: int, max_slots: int, device, dtype=torch.bfloat16, page_size: int = 64,
-                 window: Optional[int] = None):
+                 window: Optional[int] = None, chunks=None):
         """`row_widths[l]`: cache values per token of cache layer l (0: the layer caches no rows); `state_width`: fp32 state
         values per sequence, one number for all layers or one per layer (0: none).  A model whose layers run several times
-        with separate caches counts every run as a cache layer."""
+        with separate caches counts every run as a cache layer.  `window`: the largest sliding look-back of any caching layer
+        (None: unbounded); `chunks`: the chunk lengths of the caching layers when EVERY one of them reads only keys of the
+        query's own chunk (position p sees p - p mod C onwards) — then the pages before the earliest chunk start are given back."""
         self.device, self.dtype, self.page_size, self.window = torch.device(device), dtype, int(page_size), window
+        self.chunks = sorted({int(c) for c in chunks}) if chunks else None
         self.max_slots = int(max_slots)
         # every live sequence may hold one partly filled page at each end of its range
         self.num_pages = (int(max_tokens) + page_size - 1) // page_size + 2 * self.max_slots
@@ -182,9 +185,14 @@ class PagedStateCache:
 
     def release_behind(self, slot: int) -> None:
         """Give back the pages that no later token of this sequence can look at."""
-        if self.window is None:
+        if self.window is None and self.chunks is None:
             return
-        keep_from = max(0, self._len[slot] - (self.window - 1)) // self.page_size   # first page the NEXT token may read
+        nxt, first = self._len[slot], 0              # the next token's position, and the first key it (and so any later token) may read
+        if self.window is not None:
+            first = max(first, nxt - (self.window - 1))
+        if self.chunks is not None:
+            first = max(first, min(nxt - nxt % c for c in self.chunks))
+        keep_from = first // self.page_size
         for lp in range(self._first_page[slot], keep_from):
             self._free_pages.append(int(self._table_host[slot, lp % self.max_pages_per_seq]))
         self._first_page[slot] = max(self._first_page[slot], keep_from)

@@ -79,6 +79,7 @@ SYMBOLS = {
     "ktb200_quantize_activations": (_I, [_VP, _I, _L, _L, _I, _VP, _VP]),
     "ktb200_dequantize": (_I, [_VP, _I, _L, _VP, _I, _VP]),
     "ktb200_moe_gate_forward": (_I, [C.POINTER(GateConfig), _I, _VP, _VP, _VP, _VP, _VP, _VP]),
+    "ktb200_moe_gate_select": (_I, [C.POINTER(GateConfig), _I, _VP, _VP, _VP, _VP]),
     "ktb200_moe_block_forward": (_I, [C.POINTER(GateConfig), _VP, _VP, _I, _VP, _VP, _VP, _VP, _VP, _VP]),
     "ktb200_moe_block_forward_host": (_I, [C.POINTER(GateConfig), _VP, _VP, _I, _VP, _VP, _VP, _VP, _VP]),
     "ktb200_moe_forward_ep": (_I, [_VP, _VP, _I, _I, _VP, _VP, _VP, _VP, _I, _VP, _VP, _VP]),
@@ -107,7 +108,8 @@ SEQ_SYMBOLS = {
     "ktb200_last_error": (C.c_char_p, []),
     "ktb200_launch_count": (C.c_ulonglong, []),
     "ktb200_moe_gate_forward": (_I, [C.POINTER(GateConfig), _I, _VP, _VP, _VP, _VP, _VP, _VP]),
-    "ktb200_group_rmsnorm_shift": (_I, [_VP, _VP, _I, _VP, _I, _F, _VP, _VP, _I, _F, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
+    "ktb200_moe_gate_select": (_I, [C.POINTER(GateConfig), _I, _VP, _VP, _VP, _VP]),
+    "ktb200_group_rmsnorm_shift": (_I, [_VP, _VP, _I, _VP, _I, _F, _VP, _VP, _VP, _I, _F, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
     "ktb200_latent_prep": (_I, [_VP, _L, _I, _I, _I, _I, _I, _VP, _VP, _VP, _F, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP]),
     "ktb200_latent_window_attn_workspace": (C.c_size_t, [_I, _I, _I, _I]),
     "ktb200_latent_window_attn": (_I, [_VP, _VP, _I, _I, _I, _I, _I, _I, _VP, _F, _VP, _I, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP, _I, _VP]),
@@ -116,9 +118,9 @@ SEQ_SYMBOLS = {
     "ktb200_rope_rows": (_I, [_VP, _I, _I, _I, _I, _I, _VP, _VP, _VP, _I, _I, _VP]),
     "ktb200_sigmoid_gate_mul": (_I, [_VP, _VP, _L, _VP, _I, _I, _I, _I, _VP]),
     "ktb200_poly_norm": (_I, [_VP, _VP, _VP, _F, _I, _I, _I, _VP]),
-    "ktb200_experts_gate_up": (_I, [_VP, _VP, _I, _VP, _VP, _VP, _I, _I, _I, _I, _VP]),
+    "ktb200_experts_gate_up": (_I, [_VP, _VP, _I, _VP, _VP, _VP, _I, _I, _I, _I, _F, _I, _VP]),
     "ktb200_experts_down": (_I, [_VP, _VP, _VP, _I, _VP, _VP, _I, _I, _I, _I, _VP]),
-    "ktb200_experts_gate_up_by_expert": (_I, [_VP, _VP, _I, _I, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
+    "ktb200_experts_gate_up_by_expert": (_I, [_VP, _VP, _I, _I, _VP, _VP, _VP, _I, _I, _I, _I, _I, _F, _I, _VP]),
     "ktb200_experts_down_by_expert": (_I, [_VP, _VP, _VP, _I, _I, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
     # csrc/seq_mixers.cu
     "ktb200_group_rmsnorm_sandwich": (_I, [_VP, _VP, _I, _VP, _VP, _VP, _VP, _VP, _I, _F, _F, _I, _I, _I, _VP]),
@@ -130,11 +132,13 @@ SEQ_SYMBOLS = {
     "ktb200_gla_scan": (_I, [_VP, _L, _I, _I, _I, _VP, _L, _VP, _F, _I, _I, _I, _VP, _I, _I, _I, _VP, _VP, _I, _VP]),
     "ktb200_gla_out": (_I, [_VP, _VP, _F, _VP, _L, _VP, _I, _I, _I, _I, _VP]),
     "ktb200_xielu": (_I, [_VP, _VP, _VP, _L, _I, _VP]),
-    "ktb200_gated_act_mul": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
+    "ktb200_gated_act_mul": (_I, [_VP, _VP, _L, _VP, _I, _I, _I, _F, _I, _VP]),
+    "ktb200_relu_squared": (_I, [_VP, _VP, _L, _I, _VP]),
+    "ktb200_softcap": (_I, [_VP, _VP, _L, _F, _I, _VP]),
     # csrc/softmax_attn.cu, csrc/delta_rule.cu
-    "ktb200_rope_norm_cache_write": (_I, [_VP, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _VP, _I, _F, _VP, _L, _VP, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP]),
+    "ktb200_rope_norm_cache_write": (_I, [_VP, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _VP, _I, _VP, _VP, _I, _F, _VP, _L, _VP, _VP, _VP, _VP, _I, _I, _VP, _VP, _I, _I, _VP]),
     "ktb200_window_softmax_attn_workspace": (C.c_size_t, [_I, _I, _I, _I]),
-    "ktb200_window_softmax_attn": (_I, [_VP, _I, _I, _I, _I, _F, _F, _I, _VP, _VP, _VP, _I, _I, _VP, _I, _I, _VP, _VP, _I, _I, _VP, _I, _I, _VP]),
+    "ktb200_window_softmax_attn": (_I, [_VP, _I, _I, _I, _I, _F, _VP, _F, _I, _I, _VP, _VP, _VP, _I, _I, _VP, _I, _I, _VP, _VP, _I, _I, _VP, _I, _I, _VP]),
     "ktb200_window_softmax_attn_uses_tensor_cores": (_I, [_I, _I, _I, _I, _I]),
     "ktb200_window_softmax_attn_tiles": (_I, [_I, _I, _I, _I]),
     "ktb200_delta_prep": (_I, [_VP, _L, _I, _I, _I, _VP, _I, _VP, _VP, _I, _I, _I, _I, _F, _VP, _VP, _I, _VP, _L, _VP, _VP, _VP, _VP, _VP, _I, _I, _VP]),

@@ -306,6 +306,42 @@ class KSigmoidBiasAttention(torch.nn.Module):
         return torch.nn.functional.linear(o, self.o, self.o_b)
 
 
+def softmax_attention_splits(heads: int, kv_heads: int, keys: int, n_tokens: int, n_seqs: int = 0, tensor_cores: bool = False) -> int:
+    """Into how many parts `ktb200_window_softmax_attn` cuts a key range of up to `keys` keys: more than one when a small batch
+    would leave most SMs idle on a long range."""
+    if tensor_cores:
+        ctas = native.seq_lib().ktb200_window_softmax_attn_tiles(heads, kv_heads, n_tokens, n_seqs) * kv_heads
+    else:
+        ctas = n_tokens * kv_heads * ((heads // kv_heads + 7) // 8)
+    if ctas >= 148 or keys <= 256:
+        return 1
+    if tensor_cores:      # four CTAs per SM; parts of 64 keys or more
+        return max(1, min(128, keys // 64, 1184 // ctas))
+    return max(1, min(64, keys // 128, 592 // ctas))
+
+
+def paged_softmax_attention(q: torch.Tensor, kv: torch.Tensor, batch, cache, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
+                            head_scale: Optional[torch.Tensor] = None, softcap: Optional[float] = None, window: Optional[int] = None, chunk: Optional[int] = None,
+                            tensor_cores: bool = True) -> torch.Tensor:
+    """o [T, heads * vdim] = soft-max attention of the prepared queries q [T, heads, dim] over the [k | v] rows of cache layer `kv`
+    (`ktb200_window_softmax_attn`, csrc/softmax_attn.cu): the key at position j is seen from position i when j <= i,
+    i - j < window (if a window is given) and floor(j / chunk) == floor(i / chunk) (if a chunk length is given, chunks counted from the
+    sequence's position 0); scores scale * head_scale[h] * q.k, squashed to c tanh(s / c) with c = softcap; fp32 scores and weights."""
+    T, dev, dt = q.shape[0], q.device, q.dtype
+    lib, code, st = native.seq_lib(), native.GGML_BF16 if dt == torch.bfloat16 else native.GGML_F32, torch.cuda.current_stream(dev).cuda_stream
+    o = torch.empty((T, heads * vdim), dtype=dt, device=dev)
+    tc = bool(tensor_cores and batch.seqs is not None and lib.ktb200_window_softmax_attn_uses_tensor_cores(heads, kv_heads, dim, vdim, code))
+    keys = min(x for x in (window, chunk, batch.max_kv) if x)
+    splits = softmax_attention_splits(heads, kv_heads, keys, T, batch.n_seqs, tc)
+    ws = torch.empty(lib.ktb200_window_softmax_attn_workspace(T, heads, vdim, splits) // 4, dtype=torch.float32, device=dev) if splits > 1 else None
+    native.check_seq(lib.ktb200_window_softmax_attn(q.data_ptr(), heads, kv_heads, dim, vdim, float(scale), head_scale.data_ptr() if head_scale is not None else None,
+                                                    float(softcap or 0.0), int(window or 0), int(chunk or 0), batch.pos.data_ptr(), batch.slot.data_ptr(),
+                                                    batch.seqs.data_ptr() if tc else None, batch.seqs.stride(0) if tc else 0, batch.n_seqs if tc else 0,
+                                                    cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), o.data_ptr(), T, splits,
+                                                    ws.data_ptr() if ws is not None else None, code, int(tc), st))
+    return o
+
+
 class KCappedWindowAttention(torch.nn.Module):
     """Causal soft-max attention over grouped key/value heads with biased projections, a partial rotation, unit-rms queries and
     keys, capped scores, a sliding window, and values blended with another layer's values of the same token:
@@ -354,18 +390,8 @@ class KCappedWindowAttention(torch.nn.Module):
     use_tensor_cores = True
 
     def pick_splits(self, n_tokens: int, max_kv: int, n_seqs: int = 0, tensor_cores: bool = False) -> int:
-        """Cut the key range when a small batch would leave most SMs idle on a long range."""
         s = self.spec
-        keys = min(s.window, max_kv) if s.window else max_kv
-        if tensor_cores:
-            ctas = native.seq_lib().ktb200_window_softmax_attn_tiles(s.heads, s.kv_heads, n_tokens, n_seqs) * s.kv_heads
-        else:
-            ctas = n_tokens * s.kv_heads * ((s.heads // s.kv_heads + 7) // 8)
-        if ctas >= 148 or keys <= 256:
-            return 1
-        if tensor_cores:      # four CTAs per SM; parts of 64 keys or more
-            return max(1, min(128, keys // 64, 1184 // ctas))
-        return max(1, min(64, keys // 128, 592 // ctas))
+        return softmax_attention_splits(s.heads, s.kv_heads, min(s.window, max_kv) if s.window else max_kv, n_tokens, n_seqs, tensor_cores)
 
     def forward(self, h: torch.Tensor, batch, cache, cache_idx: int, v_other: Optional[torch.Tensor] = None):
         s, T, dev, dt = self.spec, h.shape[0], h.device, h.dtype
@@ -378,16 +404,71 @@ class KCappedWindowAttention(torch.nn.Module):
         q = torch.empty((T, s.heads, s.dim), dtype=dt, device=dev)
         rot_dims = s.rot.dims if s.rot is not None else 0
         native.check_seq(lib.ktb200_rope_norm_cache_write(proj.data_ptr(), self.n_in, 0, self.n_q, self.n_q + self.n_k, s.heads, s.kv_heads, s.dim, s.vdim, rot_dims,
-                                                          s.rot.layout_code if rot_dims else 0, self.inv_freq.data_ptr(), int(s.unit_rms), float(self.eps),
+                                                          s.rot.layout_code if rot_dims else 0, self.inv_freq.data_ptr(), int(s.unit_rms), None, None, 0, float(self.eps),
                                                           v_other.data_ptr() if v_other is not None else None, v_other.stride(0) if v_other is not None else 0,
                                                           self.vmix.data_ptr(), batch.pos.data_ptr(), batch.slot.data_ptr(), cache.page_table.data_ptr(),
                                                           cache.max_pages_per_seq, cache.page_size, kv.data_ptr(), q.data_ptr(), T, code, st))
-        o = torch.empty((T, s.heads * s.vdim), dtype=dt, device=dev)
-        tc = bool(self.use_tensor_cores and batch.seqs is not None and lib.ktb200_window_softmax_attn_uses_tensor_cores(s.heads, s.kv_heads, s.dim, s.vdim, code))
-        splits = self.pick_splits(T, batch.max_kv, batch.n_seqs, tc)
-        ws = torch.empty(lib.ktb200_window_softmax_attn_workspace(T, s.heads, s.vdim, splits) // 4, dtype=torch.float32, device=dev) if splits > 1 else None
-        native.check_seq(lib.ktb200_window_softmax_attn(q.data_ptr(), s.heads, s.kv_heads, s.dim, s.vdim, float(s.scale), float(s.softcap or 0.0), int(s.window or 0),
-                                                        batch.pos.data_ptr(), batch.slot.data_ptr(), batch.seqs.data_ptr() if tc else None, batch.seqs.stride(0) if tc else 0,
-                                                        batch.n_seqs if tc else 0, cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size, kv.data_ptr(),
-                                                        o.data_ptr(), T, splits, ws.data_ptr() if ws is not None else None, code, int(tc), st))
+        o = paged_softmax_attention(q, kv, batch, cache, s.heads, s.kv_heads, s.dim, s.vdim, s.scale, softcap=s.softcap, window=s.window,
+                                    tensor_cores=self.use_tensor_cores)
         return torch.nn.functional.linear(o, self.o), v_own
+
+
+class KChunkedSoftmaxAttention(torch.nn.Module):
+    """Causal soft-max attention over grouped key/value heads inside chunks of the sequence, with biased projections, queries and
+    keys normed over their whole projection, unit-rms values, a learned temperature per query head and capped scores; no position
+    enters the scores:
+
+        P       = [W_q ; W_k ; W_v] h + b                       one GEMM over the matrices that read the mixer input
+        q, k    = P[q] / sqrt(mean(P[q]^2) + eps) * w_q  (all heads of a token at once; k likewise with w_k)
+        v_g     = P[v]_g / sqrt(mean(P[v]_g^2) + eps)            head by head, no weight
+        [k | v] -> paged cache                                  ktb200_rope_norm_cache_write, all of the above in one launch
+        s_ij    = c tanh(scale t_h q_i . k_j / c), c = softcap   for j <= i with floor(j / C) == floor(i / C), C = chunk
+        o_i     = sum_j softmax_j(s_ij) v_j                     ktb200_window_softmax_attn (fp32 scores and weights)
+        out     = W_o o + b_o                                   GEMM
+
+    The chunk mask shares the attention kernels of KCappedWindowAttention (tensor-core tiles in bf16 with head sizes that are
+    multiples of 16 up to 128, CUDA cores otherwise and in fp32): a chunk is a window whose first key depends on the query's
+    position, p - p mod C.  Sizes, scale, cap and the chunk length are constructor parameters
+    (models/configuration_bilurax.ChunkedAttentionSpec); `cache_idx` picks the cache layer, so one set of weights can run several
+    times per step with separate caches.  (The reference's attention operators: archive/ktransformers/operators/attention.py.)"""
+
+    use_tensor_cores = True
+
+    def __init__(self, width: int, spec, eps: float, dtype=torch.bfloat16, device="cuda"):
+        super().__init__()
+        P = lambda *shape, dt=dtype: torch.nn.Parameter(torch.zeros(shape, dtype=dt, device=device), requires_grad=False)
+        s = self.spec = spec
+        if s.heads % s.kv_heads:
+            raise ValueError("query heads must divide into the key/value heads")
+        self.width, self.eps = width, eps
+        self.n_q, self.n_k, self.n_v = s.heads * s.dim, s.kv_heads * s.dim, s.kv_heads * s.vdim
+        self.n_in = (self.n_q + self.n_k + self.n_v + 7) // 8 * 8       # rows padded so that every row of P starts 16-byte aligned
+        self.w_in, self.b_in = P(self.n_in, width), P(self.n_in)
+        self.q_norm, self.k_norm = P(self.n_q), P(self.n_k)
+        self.temp = P(s.heads, dt=torch.float32)
+        self.o, self.o_b = P(width, s.heads * s.vdim), P(width)
+
+    def load(self, loader, prefix: str):
+        t = lambda n: loader.load_tensor(prefix + n, "cpu")
+        rows = self.n_q + self.n_k + self.n_v
+        self.w_in.data[:rows].copy_(torch.cat([t("q"), t("k"), t("v")], 0))
+        self.b_in.data[:rows].copy_(torch.cat([t("q.b"), t("k.b"), t("v.b")], 0))
+        self.q_norm.data.copy_(t("q.norm"))
+        self.k_norm.data.copy_(t("k.norm"))
+        self.temp.data.copy_(t("temp").float())
+        self.o.data.copy_(t("o"))
+        self.o_b.data.copy_(t("o.b"))
+
+    def forward(self, h: torch.Tensor, batch, cache, cache_idx: int) -> torch.Tensor:
+        s, T, dev, dt = self.spec, h.shape[0], h.device, h.dtype
+        lib, code, st = native.seq_lib(), native.GGML_BF16 if dt == torch.bfloat16 else native.GGML_F32, torch.cuda.current_stream(h.device).cuda_stream
+        kv = cache.key_cache[cache_idx]
+        proj = torch.nn.functional.linear(h, self.w_in, self.b_in)
+        q = torch.empty((T, s.heads, s.dim), dtype=dt, device=dev)
+        native.check_seq(lib.ktb200_rope_norm_cache_write(proj.data_ptr(), self.n_in, 0, self.n_q, self.n_q + self.n_k, s.heads, s.kv_heads, s.dim, s.vdim, 0, 0, None,
+                                                          2, self.q_norm.data_ptr(), self.k_norm.data_ptr(), 1, float(self.eps), None, 0, None, batch.pos.data_ptr(),
+                                                          batch.slot.data_ptr(), cache.page_table.data_ptr(), cache.max_pages_per_seq, cache.page_size, kv.data_ptr(),
+                                                          q.data_ptr(), T, code, st))
+        o = paged_softmax_attention(q, kv, batch, cache, s.heads, s.kv_heads, s.dim, s.vdim, s.scale, head_scale=self.temp, softcap=s.softcap, chunk=s.chunk,
+                                    tensor_cores=self.use_tensor_cores)
+        return torch.nn.functional.linear(o, self.o, self.o_b)

@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import ctypes as C
 from abc import ABC, abstractmethod
+from typing import Optional
 
 import numpy as np
 import torch
@@ -542,10 +543,15 @@ class KExpertsDense(nn.Module):
     by_expert_rows = 4              # most pairs whose rows such a kernel keeps in shared memory at a time
     by_expert_staged = 0            # 2 or 4 to fix that number; 0: the library chooses from the batch
 
-    def __init__(self, width: int, ff: int, experts: int, dtype=torch.bfloat16, device="cuda", gated: bool = True):
-        """`gated=False`: experts of two matrices, `W_down relu(W_up x)^2`, run by the same kernels without a gate matrix."""
+    ACTS = {"silu": 0, "gelu_tanh": 1, "clamped_glu": 2}
+
+    def __init__(self, width: int, ff: int, experts: int, dtype=torch.bfloat16, device="cuda", gated: bool = True, act: str = "silu", limit: float = 0.0):
+        """`gated=False`: experts of two matrices, `W_down relu(W_up x)^2`, run by the same kernels without a gate matrix.
+        `act` (gated experts): what becomes of g = W_gate x and u = W_up x before W_down — "silu": silu(g) u; "gelu_tanh": gelu(g) u;
+        "clamped_glu": g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit) and u' = clamp(u, -limit, limit)."""
         super().__init__()
         self.width, self.ff, self.experts, self.gated = width, ff, experts, gated
+        self.act, self.limit = self.ACTS[act], float(limit)
         self.gate = nn.Parameter(torch.empty((experts, ff, width), dtype=dtype, device=device), requires_grad=False) if gated else None
         self.up = nn.Parameter(torch.empty((experts, ff, width), dtype=dtype, device=device), requires_grad=False)
         self.down = nn.Parameter(torch.empty((experts, width, ff), dtype=dtype, device=device), requires_grad=False)
@@ -595,16 +601,26 @@ class KExpertsDense(nn.Module):
         if by_expert:
             pair_rows = torch.empty((T * top, self.width), dtype=torch.float32, device=x.device)
             native.check_seq(lib.ktb200_experts_gate_up_by_expert(x.data_ptr(), ids.data_ptr(), top, self.experts, gate_ptr, self.up.data_ptr(),
-                                                                  act.data_ptr(), T, self.width, self.ff, self.by_expert_staged, dt, st))
+                                                                  act.data_ptr(), T, self.width, self.ff, self.by_expert_staged, self.act, self.limit, dt, st))
             native.check_seq(lib.ktb200_experts_down_by_expert(act.data_ptr(), ids.data_ptr(), weights.data_ptr(), top, self.experts, self.down.data_ptr(),
                                                                pair_rows.data_ptr(), out.data_ptr(), T, self.width, self.ff, self.by_expert_staged, dt, st))
             return out
         native.check_seq(lib.ktb200_experts_gate_up(x.data_ptr(), ids.data_ptr(), top, gate_ptr, self.up.data_ptr(), act.data_ptr(), T, self.width,
-                                                    self.ff, dt, st))
+                                                    self.ff, self.act, self.limit, dt, st))
         native.check_seq(lib.ktb200_experts_down(act.data_ptr(), ids.data_ptr(), weights.data_ptr(), top, self.down.data_ptr(), out.data_ptr(), T, self.width,
                                                  self.ff, dt, st))
         return out
 
+
+    def _activate(self, g: Optional[torch.Tensor], u: torch.Tensor) -> torch.Tensor:
+        """the experts' activation over whole GEMM outputs [pairs, ff]: one elementwise launch, fp32 inside"""
+        lib, st, out = native.seq_lib(), _stream(u.device), torch.empty_like(u)
+        if g is None:
+            native.check_seq(lib.ktb200_relu_squared(u.data_ptr(), out.data_ptr(), u.numel(), TORCH_TO_GGML_HIDDEN[u.dtype], st))
+        else:
+            native.check_seq(lib.ktb200_gated_act_mul(g.data_ptr(), u.data_ptr(), self.ff, out.data_ptr(), u.shape[0], self.ff, self.act, self.limit,
+                                                      TORCH_TO_GGML_HIDDEN[u.dtype], st))
+        return out
 
     def forward_grouped(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         T, top = ids.shape
@@ -616,18 +632,17 @@ class KExpertsDense(nn.Module):
         if x.dtype == torch.bfloat16 and self.width % 8 == 0 and self.ff % 8 == 0 and hasattr(F, "grouped_mm"):
             # the library's grouped GEMM takes the segment ends on the device: no host read of the routing, three launches
             offs = counts.cumsum(0).to(torch.int32)
-            u = F.grouped_mm(xs, self.up.transpose(1, 2), offs=offs).float()
-            a = F.silu(F.grouped_mm(xs, self.gate.transpose(1, 2), offs=offs).float()) * u if self.gated else torch.relu(u).square()
-            y = F.grouped_mm(a.to(x.dtype), self.down.transpose(1, 2), offs=offs)
+            u = F.grouped_mm(xs, self.up.transpose(1, 2), offs=offs)
+            a = self._activate(F.grouped_mm(xs, self.gate.transpose(1, 2), offs=offs) if self.gated else None, u)
+            y = F.grouped_mm(a, self.down.transpose(1, 2), offs=offs)
         else:
             y = torch.empty((T * top, self.width), dtype=x.dtype, device=x.device)
             lo = 0
             for e, n in enumerate(counts.tolist()):                              # one host read of a step's routing
                 if n:
                     seg = xs[lo:lo + n]
-                    u = F.linear(seg, self.up[e]).float()
-                    a = F.silu(F.linear(seg, self.gate[e]).float()) * u if self.gated else torch.relu(u).square()
-                    y[lo:lo + n] = F.linear(a.to(x.dtype), self.down[e])
+                    a = self._activate(F.linear(seg, self.gate[e]) if self.gated else None, F.linear(seg, self.up[e]))
+                    y[lo:lo + n] = F.linear(a, self.down[e])
                     lo += n
         pairs = torch.empty_like(y)
         pairs[order] = y
@@ -665,6 +680,26 @@ class KTopKSoftmaxMoE(nn.Module):
     def load(self, loader, prefix: str):
         self.router.load(loader, prefix + "router")
         self.experts.load(loader, prefix, names=(None, "up", "down"))
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        ids, w = self.router(h)
+        return self.experts(h, ids, w)
+
+
+class KGroupedSigmoidMoE(nn.Module):
+    """router (operators/gate.KGroupedSigmoidGate: sigmoid scores, a correction that only steers the choice, experts chosen inside
+    the best groups, weights normalised over the chosen and scaled) -> dense gated experts with the clamped sigmoid activation
+    (`g' sigmoid(1.702 g') (u' + 1)`, `limit` the clamp): a mixture-of-experts feed-forward without shared experts."""
+
+    def __init__(self, width: int, ff: int, experts: int, top: int, groups: int, keep_groups: int, out_scale: float, limit: float, dtype=torch.bfloat16, device="cuda"):
+        super().__init__()
+        from .gate import KGroupedSigmoidGate
+        self.router = KGroupedSigmoidGate(width, experts, top, groups, keep_groups, out_scale, device=device)
+        self.experts = KExpertsDense(width, ff, experts, dtype=dtype, device=device, act="clamped_glu", limit=limit)
+
+    def load(self, loader, prefix: str):
+        self.router.load(loader, prefix + "router", prefix + "correction")
+        self.experts.load(loader, prefix)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         ids, w = self.router(h)

@@ -156,3 +156,43 @@ class KTopKSoftmaxGate(nn.Module):
         native.check_seq(native.seq_lib().ktb200_moe_gate_forward(C.byref(cfg), n, x.data_ptr(), idx.data_ptr(), wt.data_ptr(), None, None,
                                                                   torch.cuda.current_stream(x.device).cuda_stream))
         return idx, wt
+
+
+class KGroupedSigmoidGate(nn.Module):
+    """Sigmoid scores s = sigmoid(W x) in fp32; experts are CHOSEN by s + correction among the experts of the `keep_groups` groups
+    (of experts / groups neighbours) whose two largest choice scores sum highest, every other expert counting as minus infinity;
+    the WEIGHTS are the chosen experts' s, divided by their sum (+ 1e-20) and multiplied by `out_scale`: the router kernel's
+    `scoring = sigmoid, topk_method = noaux_tc, norm_topk_prob = 1` case (DeepSeek-V3's gate,
+    archive/ktransformers/models/modeling_deepseek_v3.py:430-481), as a plain module for models that are built on the operators
+    directly.  Decode-sized batches run the one-launch router kernel (fp32 GEMV + selection); from `gemm_min_tokens` tokens the
+    logits are one fp32 library GEMM (TF32 off) and the selection is `ktb200_moe_gate_select`, a CTA per token."""
+
+    gemm_min_tokens = 48
+
+    def __init__(self, width: int, experts: int, top: int, groups: int, keep_groups: int, out_scale: float, device="cuda"):
+        super().__init__()
+        if experts % groups or not (1 <= keep_groups <= groups) or top > keep_groups * (experts // groups):
+            raise ValueError(f"router: {experts} experts do not divide into {groups} groups of which {keep_groups} hold {top} choices")
+        if experts > 512 or top > 32 or groups > 32:
+            raise ValueError("router: at most 512 experts, 32 groups and 32 choices per token")
+        self.width, self.experts, self.top, self.groups, self.keep_groups, self.out_scale = width, experts, top, groups, keep_groups, float(out_scale)
+        self.weight = nn.Parameter(torch.empty((experts, width), dtype=torch.float32, device=device), requires_grad=False)
+        self.correction = nn.Parameter(torch.zeros(experts, dtype=torch.float32, device=device), requires_grad=False)
+
+    def load(self, loader, key: str, correction_key: str):
+        self.weight.data.copy_(loader.load_tensor(key, "cpu").float())
+        self.correction.data.copy_(loader.load_tensor(correction_key, "cpu").float())
+
+    def forward(self, x: torch.Tensor):
+        n = x.shape[0]
+        idx = torch.empty((n, self.top), dtype=torch.int64, device=x.device)
+        wt = torch.empty((n, self.top), dtype=torch.float32, device=x.device)
+        cfg = native.GateConfig(self.experts, self.width, self.top, self.groups, self.keep_groups, _SCORING["sigmoid"], _TOPK["noaux_tc"], 1, self.out_scale,
+                                self.weight.data_ptr(), self.correction.data_ptr(), TORCH_TO_GGML_HIDDEN[x.dtype])
+        st = torch.cuda.current_stream(x.device).cuda_stream
+        if n >= self.gemm_min_tokens or self.width % 4:
+            logits = nn.functional.linear(x.float(), self.weight)
+            native.check_seq(native.seq_lib().ktb200_moe_gate_select(C.byref(cfg), n, logits.data_ptr(), idx.data_ptr(), wt.data_ptr(), st))
+        else:
+            native.check_seq(native.seq_lib().ktb200_moe_gate_forward(C.byref(cfg), n, x.data_ptr(), idx.data_ptr(), wt.data_ptr(), None, None, st))
+        return idx, wt

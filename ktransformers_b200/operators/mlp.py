@@ -85,6 +85,27 @@ class KGatedMLP(nn.Module):
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         gu = F.linear(h, self.gate_up)
         a = torch.empty((h.shape[0], self.ff), dtype=gu.dtype, device=gu.device)
-        native.check_seq(native.seq_lib().ktb200_gated_act_mul(gu.data_ptr(), a.data_ptr(), gu.shape[0], self.ff, self.act, GGML_OF[gu.dtype],
-                                                               torch.cuda.current_stream(gu.device).cuda_stream))
+        native.check_seq(native.seq_lib().ktb200_gated_act_mul(gu.data_ptr(), gu.data_ptr() + self.ff * gu.element_size(), 2 * self.ff, a.data_ptr(), gu.shape[0], self.ff,
+                                                               self.act, 0.0, GGML_OF[gu.dtype], torch.cuda.current_stream(gu.device).cuda_stream))
+        return F.linear(a, self.down)
+
+
+class KReluSquaredMLP(nn.Module):
+    """A two-matrix feed-forward without biases, W_down relu(W_up h)^2.  The two products are library GEMMs; the activation is one
+    `ktb200_relu_squared` launch (csrc/seq_mixers.cu, fp32 inside, one rounding to the compute dtype)."""
+
+    def __init__(self, width: int, ff: int, dtype=torch.bfloat16, device="cuda"):
+        super().__init__()
+        self.width, self.ff = width, ff
+        self.up = nn.Parameter(torch.empty((ff, width), dtype=dtype, device=device), requires_grad=False)
+        self.down = nn.Parameter(torch.empty((width, ff), dtype=dtype, device=device), requires_grad=False)
+
+    def load(self, loader, prefix: str):
+        self.up.data.copy_(loader.load_tensor(prefix + "up", "cpu"))
+        self.down.data.copy_(loader.load_tensor(prefix + "down", "cpu"))
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        z = F.linear(h, self.up)
+        a = torch.empty_like(z)
+        native.check_seq(native.seq_lib().ktb200_relu_squared(z.data_ptr(), a.data_ptr(), z.numel(), GGML_OF[z.dtype], torch.cuda.current_stream(z.device).cuda_stream))
         return F.linear(a, self.down)

@@ -2,7 +2,8 @@
 
 One launch of `ktb200_group_rmsnorm_shift` (csrc/seq_ops.cu) per call:
 
-    x_out = x_in + mult * (a + b)                         (when the previous layer's branch outputs are passed in)
+    x_out = x_in + mult * (a + b) + row                   (a, b: the previous layer's branch outputs, when passed in; row: one
+                                                           vector added to every token, e.g. the step vector of a looped pass)
     h     = x_out / sqrt(mean_g(x_out^2) + eps) * weight   per group g of `groups` equal consecutive parts, fp32
     hs_t  = h_t + (h_{t-1} - h_t) * shift                  (layers that mix in the previous token's normed row)
 
@@ -40,11 +41,14 @@ class KGroupRMSNormShift(nn.Module):
         if self.shift is not None:
             self.shift.data.copy_(loader.load_tensor(shift_key, "cpu"))
 
-    def forward(self, x: torch.Tensor, delta_a=None, delta_b=None, mult: float = 1.0, batch=None, state: Optional[torch.Tensor] = None, want_h: bool = True):
-        """x [T, width] fp32.  Returns (residual after the sum, h or None, hs or None)."""
+    def forward(self, x: torch.Tensor, delta_a=None, delta_b=None, mult: float = 1.0, batch=None, state: Optional[torch.Tensor] = None, want_h: bool = True,
+                row_add: Optional[torch.Tensor] = None):
+        """x [T, width] fp32; delta_a / delta_b [T, width] fp32 or the compute dtype; row_add [width] fp32.  Returns (residual after
+        the sum, h or None, hs or None)."""
         T = x.shape[0]
         dt = self.weight.dtype
-        add = delta_a is not None or delta_b is not None
+        add = delta_a is not None or delta_b is not None or row_add is not None
+        assert row_add is None or (row_add.dtype == torch.float32 and row_add.is_contiguous() and row_add.shape == (self.width,))
         x_out = torch.empty_like(x) if add else x
         h = torch.empty((T, self.width), dtype=dt, device=x.device) if want_h else None
         hs = torch.empty((T, self.width), dtype=dt, device=x.device) if self.shift is not None else None
@@ -52,7 +56,7 @@ class KGroupRMSNormShift(nn.Module):
             assert d is None or (d.is_contiguous() and d.shape == x.shape)
         native.check_seq(native.seq_lib().ktb200_group_rmsnorm_shift(
             x.data_ptr(), _ptr(delta_a), GGML_OF[delta_a.dtype] if delta_a is not None else 0, _ptr(delta_b),
-            GGML_OF[delta_b.dtype] if delta_b is not None else 0, float(mult), x_out.data_ptr() if add else None, self.weight.data_ptr(), self.groups,
+            GGML_OF[delta_b.dtype] if delta_b is not None else 0, float(mult), _ptr(row_add), x_out.data_ptr() if add else None, self.weight.data_ptr(), self.groups,
             float(self.eps), _ptr(self.shift), _ptr(batch.prev_idx) if hs is not None else None, _ptr(batch.rd_row) if hs is not None else None,
             _ptr(batch.wr_row) if hs is not None else None, _ptr(state) if hs is not None else None, _ptr(h), _ptr(hs), T, self.width, GGML_OF[dt],
             torch.cuda.current_stream(x.device).cuda_stream))

@@ -279,7 +279,7 @@ def kernel_leg(flush, peak_gbs, have_main_lib):
         ids = torch.stack([torch.randperm(E, generator=g, device=dev)[:top] for _ in range(T)]).to(torch.int64)
         wts = torch.rand(T, top, generator=g, device=dev)
         act, out = torch.empty(T * top, ff, dtype=bf, device=dev), torch.empty(T, D, device=dev)
-        f1 = lambda: native.check_seq(seq.ktb200_experts_gate_up(x.data_ptr(), ids.data_ptr(), top, Wg.data_ptr(), Wu.data_ptr(), act.data_ptr(), T, D, ff, 30, S()))
+        f1 = lambda: native.check_seq(seq.ktb200_experts_gate_up(x.data_ptr(), ids.data_ptr(), top, Wg.data_ptr(), Wu.data_ptr(), act.data_ptr(), T, D, ff, 0, 0.0, 30, S()))
         f2 = lambda: native.check_seq(seq.ktb200_experts_down(act.data_ptr(), ids.data_ptr(), wts.data_ptr(), top, Wd.data_ptr(), out.data_ptr(), T, D, ff, 30, S()))
         uniq = len(set(ids.flatten().tolist()))                            # every chosen expert is read from HBM at least once
         row("experts_gate_up_kernel", f"T={T} top={top} width={D} ff={ff} bf16", timed(f1, flush), uniq * 2 * ff * D * 2,
@@ -291,7 +291,7 @@ def kernel_leg(flush, peak_gbs, have_main_lib):
         ids = torch.stack([torch.randperm(E, generator=g, device=dev)[:top] for _ in range(T)]).to(torch.int64)
         wts = torch.rand(T, top, generator=g, device=dev)
         act, out, pair_rows = torch.empty(T * top, ff, dtype=bf, device=dev), torch.empty(T, D, device=dev), torch.empty(T * top, D, device=dev)
-        f1 = lambda: native.check_seq(seq.ktb200_experts_gate_up_by_expert(x.data_ptr(), ids.data_ptr(), top, E, Wg.data_ptr(), Wu.data_ptr(), act.data_ptr(), T, D, ff, 0, 30, S()))
+        f1 = lambda: native.check_seq(seq.ktb200_experts_gate_up_by_expert(x.data_ptr(), ids.data_ptr(), top, E, Wg.data_ptr(), Wu.data_ptr(), act.data_ptr(), T, D, ff, 0, 0, 0.0, 30, S()))
         f2 = lambda: native.check_seq(seq.ktb200_experts_down_by_expert(act.data_ptr(), ids.data_ptr(), wts.data_ptr(), top, E, Wd.data_ptr(), pair_rows.data_ptr(), out.data_ptr(),
                                                                         T, D, ff, 0, 30, S()))
         uniq = len(set(ids.flatten().tolist()))
@@ -433,8 +433,8 @@ def mabidra_kernel_leg(flush, peak_gbs, peak_tflops):
         ids = torch.stack([torch.randperm(E, generator=g, device=dev)[:top] for _ in range(T)]).to(torch.int64)
         act = torch.empty(T * top, ff, dtype=bf, device=dev)
         uniq = len(set(ids.flatten().tolist()))
-        ours = timed(lambda: native.check_seq(seq.ktb200_experts_gate_up_by_expert(x.data_ptr(), ids.data_ptr(), top, E, None, Wu.data_ptr(), act.data_ptr(), T, D, ff, 0, 30, S())), flush)
-        ms = timed(lambda: native.check_seq(seq.ktb200_experts_gate_up_by_expert(x.data_ptr(), ids.data_ptr(), top, E, Wg.data_ptr(), Wu.data_ptr(), act.data_ptr(), T, D, ff, 0, 30, S())), flush)
+        ours = timed(lambda: native.check_seq(seq.ktb200_experts_gate_up_by_expert(x.data_ptr(), ids.data_ptr(), top, E, None, Wu.data_ptr(), act.data_ptr(), T, D, ff, 0, 0, 0.0, 30, S())), flush)
+        ms = timed(lambda: native.check_seq(seq.ktb200_experts_gate_up_by_expert(x.data_ptr(), ids.data_ptr(), top, E, Wg.data_ptr(), Wu.data_ptr(), act.data_ptr(), T, D, ff, 0, 0, 0.0, 30, S())), flush)
         row("experts_gate_up_by_expert_kernel (no gate, relu^2)", f"T={T} top={top} width={D} ff={ff} bf16", ours, nbytes=uniq * ff * D * 2,
             peer={"kernel": "experts_gate_up_by_expert_kernel (gated)", "us": ms * 1e3, "frac_of_measured_hbm": uniq * 2 * ff * D * 2 / ms / 1e6 / peak_gbs})
     return rows
@@ -586,7 +586,7 @@ def zivulix_kernel_leg(flush, peak_gbs, peak_tflops):
     # ---- activation
     for T, ff in ((8, 18432), (2048, 18432)):
         gu, oo, zz, pq = rn(T, 2 * ff), torch.empty(T, ff, dtype=bf, device=dev), rn(T, ff), torch.tensor([0.3, -0.2], device=dev)
-        ours = timed(lambda: native.check_seq(seq.ktb200_gated_act_mul(gu.data_ptr(), oo.data_ptr(), T, ff, 1, 30, S())), flush)
+        ours = timed(lambda: native.check_seq(seq.ktb200_gated_act_mul(gu.data_ptr(), gu.data_ptr() + 2 * ff, 2 * ff, oo.data_ptr(), T, ff, 1, 0.0, 30, S())), flush)
         ms = timed(lambda: native.check_seq(seq.ktb200_xielu(zz.data_ptr(), oo.data_ptr(), pq.data_ptr(), zz.numel(), 30, S())), flush)
         row("gated_act_mul_kernel (gelu_tanh)", f"T={T} ff={ff}", ours, nbytes=T * ff * 6, peer=peer_of("xielu_kernel", ms, T * ff * 4))
     return rows
