@@ -2,7 +2,7 @@
 """bench.py — decode tok/s of the quantized-MoE hot path at DeepSeek-V3 shapes.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
-    python bench.py --model lekapel|mabidra|zivulix [--sizes 2k-wide,v3-layer]     (other workloads: see ktransformers_b200/util/model_bench.py)
+    python bench.py --model lekapel|mabidra|zivulix|bilurax [--sizes 2k-wide,v3-layer]     (other workloads: see ktransformers_b200/util/model_bench.py)
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 Workload (config.workload): DeepSeek-V3 671B Q4_K_M single-stream decode, the MoE-block hot path of every
@@ -428,7 +428,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=4096, help="cached tokens per sequence in the whole-step leg")
     ap.add_argument("--no-full-step", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 1024-token grouped-GEMM leg")
-    ap.add_argument("--model", default=None, choices=["lekapel", "mabidra", "zivulix"],
+    ap.add_argument("--model", default=None, choices=["lekapel", "mabidra", "zivulix", "bilurax"],
                     help="instead of the default workload: prefill / decode throughput and per-kernel rooflines of that model family "
                          "(random weights) beside the DeepSeek path's kernels at equal size")
     ap.add_argument("--sizes", default=None, help="with --model: comma-separated size names (default: all)")

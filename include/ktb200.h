@@ -191,7 +191,7 @@ int ktb200_dequantize(const void* src_dev, int ggml_type, long n_elements, void*
  * topk_softmax (kt-kernel/cuda/moe/moe_topk_softmax_kernels.cu:405-462).
  *   logits = x(fp32) . W^T (fp32) ; scores = sigmoid | softmax ; noaux_tc: s' = scores + bias,
  *   group score = sum of top-2 s' in the group, keep topk_group groups, top_k experts by s',
- *   weights = scores[idx] (normalised if norm_topk_prob) * routed_scaling_factor.
+ *   weights = scores[idx] (normalised if norm_topk_prob; 1: only when top_k > 1, as the reference does; 2: always) * routed_scaling_factor.
  * ------------------------------------------------------------------------------------------ */
 typedef struct ktb200_gate_config {
     int n_experts;             /* n_routed_experts */

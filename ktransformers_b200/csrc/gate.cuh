@@ -222,7 +222,8 @@ __device__ void gate_select_token(const GateParams& pin, int t, float* sm, int64
         // V2 (modeling_deepseek.py:455-459): normalise XOR scale.
         if (lane < p.top_k) {
             float w = myw;
-            const bool do_norm = (p.top_k > 1 && p.norm_topk_prob) || p.scoring == 2;    // soft-max over one chosen logit is 1
+            // (norm_topk_prob 2: a single chosen expert is normalised too, so its weight is the scaling factor alone)
+            const bool do_norm = (p.top_k > 1 && p.norm_topk_prob) || p.norm_topk_prob == 2 || p.scoring == 2;    // soft-max over one chosen logit is 1
             if (do_norm) w = __fdiv_rn(w, wsum + 1e-20f);
             if (p.topk_method == 0 || !do_norm) w = w * p.routed_scaling_factor;
             idx_out[lane] = myidx;

@@ -162,8 +162,9 @@ class KGroupedSigmoidGate(nn.Module):
     """Sigmoid scores s = sigmoid(W x) in fp32; experts are CHOSEN by s + correction among the experts of the `keep_groups` groups
     (of experts / groups neighbours) whose two largest choice scores sum highest, every other expert counting as minus infinity;
     the WEIGHTS are the chosen experts' s, divided by their sum (+ 1e-20) and multiplied by `out_scale`: the router kernel's
-    `scoring = sigmoid, topk_method = noaux_tc, norm_topk_prob = 1` case (DeepSeek-V3's gate,
-    archive/ktransformers/models/modeling_deepseek_v3.py:430-481), as a plain module for models that are built on the operators
+    `scoring = sigmoid, topk_method = noaux_tc` case (DeepSeek-V3's gate, archive/ktransformers/models/modeling_deepseek_v3.py:430-481)
+    with `norm_topk_prob = 2`: the weights are normalised also when a token uses ONE expert (whose weight is then `out_scale`; the
+    reference's gate leaves a single choice un-normalised), as a plain module for models that are built on the operators
     directly.  Decode-sized batches run the one-launch router kernel (fp32 GEMV + selection); from `gemm_min_tokens` tokens the
     logits are one fp32 library GEMM (TF32 off) and the selection is `ktb200_moe_gate_select`, a CTA per token."""
 
@@ -187,7 +188,7 @@ class KGroupedSigmoidGate(nn.Module):
         n = x.shape[0]
         idx = torch.empty((n, self.top), dtype=torch.int64, device=x.device)
         wt = torch.empty((n, self.top), dtype=torch.float32, device=x.device)
-        cfg = native.GateConfig(self.experts, self.width, self.top, self.groups, self.keep_groups, _SCORING["sigmoid"], _TOPK["noaux_tc"], 1, self.out_scale,
+        cfg = native.GateConfig(self.experts, self.width, self.top, self.groups, self.keep_groups, _SCORING["sigmoid"], _TOPK["noaux_tc"], 2, self.out_scale,
                                 self.weight.data_ptr(), self.correction.data_ptr(), TORCH_TO_GGML_HIDDEN[x.dtype])
         st = torch.cuda.current_stream(x.device).cuda_stream
         if n >= self.gemm_min_tokens or self.width % 4:

@@ -1,6 +1,6 @@
 """Throughput and per-kernel rooflines of a step-function model at layer sizes of real models, with random weights, beside
 the closest existing model's kernels at equal size (`bench.py --model lekapel`, `bench.py --model mabidra`,
-`bench.py --model zivulix`).
+`bench.py --model zivulix`, `bench.py --model bilurax`).
 
 Two parts:
   * end to end through the Engine (scheduler, paged cache, step function): prompt tokens/s for a long prompt cut into portions,
@@ -77,6 +77,36 @@ def make_zivulix_config(s):
             "layers": [{"type": kinds[c][0], "mixer": kinds[c][1], "mlp": {"kind": "dense", "ff": s["dense_ff"]}} for c in s["order"]]}
 
 
+BILURAX_SIZES = {
+    # the same widths, feed-forward sizes, expert counts and layer-run counts as MABIDRA_SIZES (6 layer runs for 5 layers / 3 for 2, the first
+    # layer dense, the others mixtures of experts, the span `loop` running twice); every mixer is chunked soft-max attention over the grouped
+    # heads of Mabidra's attention layers.  The chunk is as long as the benchmark's context, and `ctx` puts the decoded token at a chunk's last
+    # position, so that a decode step reads as many keys as Mabidra's attention does.  The closest existing model at equal size is Mabidra with
+    # sigmoid attention in every layer (its experts have two matrices where these have three).
+    "2k-wide": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, chunk=2048, dense_ff=8192, experts=32, top=4, groups=4, keep=2, ff=1024, vocab=32768, n_layers=5,
+                    loop=(1, 2, 2), ctx=2047, rank=64),
+    "v3-layer": dict(width=7168, heads=64, kv_heads=8, dim=128, vdim=128, chunk=4096, dense_ff=18432, experts=32, top=8, groups=4, keep=2, ff=2048, vocab=32768, n_layers=2,
+                     loop=(1, 2, 2), ctx=4095, rank=128),
+}
+
+
+def make_bilurax_config(s):
+    attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5, "softcap": 30.0, "mask": {"size": s["chunk"]}}
+    moe = {"kind": "moe", "expert": {"ff": s["ff"], "limit": 7.0}, "router": {"experts": s["experts"], "top": s["top"], "groups": {"count": s["groups"], "keep": s["keep"]}, "scale": 2.0}}
+    layers = [{"type": "attention", "mixer": attn, "mlp": {"kind": "dense", "ff": s["dense_ff"]} if i == 0 else moe} for i in range(s["n_layers"])]
+    return {"architecture": "Bilurax", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "logit_softcap": 50.0, "layers": layers,
+            "loop": {"start": s["loop"][0], "stop": s["loop"][1], "times": s["loop"][2]}}
+
+
+def make_mabidra_attn_config(s):
+    """Mabidra at the sizes of a Bilurax size entry: sigmoid attention in every layer, the same dense and expert feed-forward sizes, the same loop"""
+    attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5, "bias_max": 1024, "q_temp": {"coef": 0.1, "every": 512}}
+    moe = {"kind": "moe", "expert": {"ff": s["ff"]}, "router": {"experts": s["experts"], "top": s["top"]}}
+    layers = [{"type": "attention", "mixer": attn, "mlp": {"kind": "dense", "ff": s["dense_ff"]} if i == 0 else moe} for i in range(s["n_layers"])]
+    return {"architecture": "Mabidra", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5, "groups": 4}, "embedding": {"scale": 1.0}, "layers": layers,
+            "loop": {"start": s["loop"][0], "stop": s["loop"][1], "times": s["loop"][2]}}
+
+
 def make_mabidra_dense_config(s):
     """Mabidra at the sizes of a Zivulix size entry: sigmoid attention for A and L, gated linear attention for D, dense feed-forwards"""
     attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5, "bias_max": 1024, "q_temp": {"coef": 0.1, "every": 512}}
@@ -86,7 +116,11 @@ def make_mabidra_dense_config(s):
 
 
 def random_model(cfg_dict, dtype=torch.bfloat16, device="cuda", size=None):
-    if cfg_dict["architecture"] == "Zivulix":
+    if cfg_dict["architecture"] == "Bilurax":
+        from ..models.configuration_bilurax import BiluraxConfig
+        from ..models.modeling_bilurax import BiluraxForCausalLM
+        model = BiluraxForCausalLM(BiluraxConfig.from_dict(cfg_dict), dtype=dtype, device=device)
+    elif cfg_dict["architecture"] == "Zivulix":
         from ..models.configuration_zivulix import ZivulixConfig
         from ..models.modeling_zivulix import ZivulixForCausalLM
         model = ZivulixForCausalLM(ZivulixConfig.from_dict(cfg_dict), dtype=dtype, device=device)
@@ -146,7 +180,8 @@ def timed(fn, flush, iters=10, warmup=3):
 
 def engine_leg(name, size, flush, steps, warmup, family="lekapel"):
     from .engine import Engine
-    cfg = {"lekapel": make_config, "mabidra": make_mabidra_config, "zivulix": make_zivulix_config, "mabidra-dense": make_mabidra_dense_config}[family](size)
+    cfg = {"lekapel": make_config, "mabidra": make_mabidra_config, "zivulix": make_zivulix_config, "mabidra-dense": make_mabidra_dense_config,
+           "bilurax": make_bilurax_config, "mabidra-attn": make_mabidra_attn_config}[family](size)
     model = random_model(cfg, size=size)
     if family == "zivulix":      # norm weights are zero-centred, decays and the value blend inside their usual ranges
         for pname, p in model.named_parameters():
@@ -592,6 +627,179 @@ def zivulix_kernel_leg(flush, peak_gbs, peak_tflops):
     return rows
 
 
+def bilurax_kernel_leg(flush, peak_gbs, peak_tflops):
+    """The kernels of the Bilurax operators at real layer sizes (bf16), each beside the like kernel of the closest existing path."""
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    seq = native.seq_lib()
+    S = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+    rows = []
+    g = torch.Generator(device=dev).manual_seed(7)
+    rn = lambda *s, dt=bf: torch.randn(*s, generator=g, device=dev, dtype=torch.float32).to(dt)
+
+    def peer_of(kernel, ms, nbytes=None, flops=None):
+        r = {"kernel": kernel, "us": ms * 1e3}
+        if nbytes is not None:
+            r["frac_of_measured_hbm"] = nbytes / ms / 1e6 / peak_gbs
+        if flops is not None:
+            r.update(TFLOPs=flops / ms / 1e9, frac_of_measured_bf16=flops / ms / 1e9 / peak_tflops)
+        return r
+
+    def row(kernel, what, ms, nbytes=None, flops=None, peer=None):
+        r = dict(peer_of(kernel, ms, nbytes, flops), case=what)
+        if nbytes is not None:
+            r["GBps"] = nbytes / ms / 1e6
+        progress(f"{kernel} {what}: {ms * 1e3:.1f} us")
+        if peer:
+            r["closest"] = peer
+        rows.append(r)
+
+    D = 7168
+    from ..operators.norm import KGroupRMSNormShift
+    for T in (1, 8, 2048):      # a pass opening: x + y + x0 + step, norm, shift  vs  Lekapel's x + m (a + b), norm in 4 groups, shift
+        x, y, x0, step = rn(T, D, dt=torch.float32), rn(T, D), rn(T, D, dt=torch.float32), rn(D, dt=torch.float32)
+        state = torch.zeros(2, D, device=dev)
+        meta = torch.zeros(5, T, dtype=torch.int32, device=dev)
+        meta[2] = torch.arange(-1, T - 1, dtype=torch.int32, device=dev)
+        meta[3], meta[4] = -1, -1
+        batch = type("B", (), {"prev_idx": meta[2], "rd_row": meta[3], "wr_row": meta[4]})()
+        mine, theirs = KGroupRMSNormShift(D, 1, 1e-6, True), KGroupRMSNormShift(D, 4, 1e-5, True)
+        ours = timed(lambda: mine(x, y, x0, 1.0, batch, state, want_h=False, row_add=step), flush)
+        ms = timed(lambda: theirs(x, y, y, 0.6, batch, state, want_h=True), flush)
+        row("group_norm_shift_kernel (two addends of which one fp32, a row vector, shifted output only)", f"T={T} width={D}", ours, nbytes=T * D * (4 + 2 + 4 + 4 + 2),
+            peer=peer_of("group_norm_shift_kernel (two bf16 addends, 4 groups, both outputs)", ms, T * D * (4 + 2 + 2 + 4 + 2 + 2)))
+
+    # ---- attention: 64 query heads on 8 key/value heads of 128 + 128 values
+    H, G, d, dv, PAGE = 64, 8, 128, 128, 64
+    cw, n_in = G * (d + dv), (64 + 8) * 128 + 8 * 128
+    inv = torch.arange(d // 4, dtype=torch.float64, device=dev).mul(-4.0 / d).exp2() / 4.0
+    lam = torch.tensor([0.3], device=dev)
+    for T in (8, 2048):         # row-wide weighted q / k norms + value unit rms + cache write  vs  rotation + per-head unit rms + value blend + cache write
+        pages = (T + PAGE - 1) // PAGE
+        proj, vo, cache, qo = rn(T, n_in), rn(T, G * dv), rn(pages + 1, PAGE, cw), torch.empty(T, H, d, dtype=bf, device=dev)
+        qw, kw = rn(H * d), rn(G * d)
+        ptab = torch.arange(pages, dtype=torch.int32, device=dev).reshape(1, pages)
+        pos, slot = torch.arange(T, dtype=torch.int32, device=dev), torch.zeros(T, dtype=torch.int32, device=dev)
+        ours = timed(lambda: native.check_seq(seq.ktb200_rope_norm_cache_write(proj.data_ptr(), n_in, 0, H * d, (H + G) * d, H, G, d, dv, 0, 0, None, 2, qw.data_ptr(), kw.data_ptr(), 1,
+                                                                               1e-6, None, 0, None, pos.data_ptr(), slot.data_ptr(), ptab.data_ptr(), pages, PAGE, cache.data_ptr(),
+                                                                               qo.data_ptr(), T, 30, S())), flush)
+        ms = timed(lambda: native.check_seq(seq.ktb200_rope_norm_cache_write(proj.data_ptr(), n_in, 0, H * d, (H + G) * d, H, G, d, dv, d // 2, 1, inv.data_ptr(), 1, None, None, 0, 1e-6,
+                                                                             vo.data_ptr(), G * dv, lam.data_ptr(), pos.data_ptr(), slot.data_ptr(), ptab.data_ptr(), pages, PAGE,
+                                                                             cache.data_ptr(), qo.data_ptr(), T, 30, S())), flush)
+        nb = T * (n_in + H * d + cw) * 2
+        row("rope_norm_cache_write_kernel (row-wide q/k norms, unit-rms values)", f"T={T} heads={H}/{G} dim={d}", ours, nbytes=nb,
+            peer=peer_of("rope_norm_cache_write_kernel (rotation, per-head unit rms, value blend)", ms, nb + T * G * dv * 2))
+
+    from ..operators.attention import softmax_attention_splits
+    temp = 0.5 + torch.rand(H, device=dev)
+    for B, ctx in ((1, 4096), (8, 4096), (1, 32768)):      # the chunk mask with a head temperature  vs  the window mask of the same kernel
+        pages = (ctx + PAGE - 1) // PAGE
+        cache = rn(B * pages + 1, PAGE, cw)
+        ptab = torch.arange(B * pages, dtype=torch.int32, device=dev).reshape(B, pages)
+        q, out = rn(B, H, d), torch.empty(B, H * dv, dtype=bf, device=dev)
+        pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+        slot = torch.arange(B, dtype=torch.int32, device=dev)
+        seqs = torch.tensor([list(range(B)), [1] * B, [-1] * B, [-1] * B], dtype=torch.int32, device=dev)
+        nb = B * ctx * cw * 2
+        for tc in (1, 0):
+            splits = softmax_attention_splits(H, G, ctx, B, B, bool(tc))
+            ws2 = torch.empty(max(1, seq.ktb200_window_softmax_attn_workspace(B, H, dv, splits) // 4), device=dev)
+            fn = lambda hs, win, ch: native.check_seq(seq.ktb200_window_softmax_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, hs, 30.0, win, ch, pos.data_ptr(), slot.data_ptr(),
+                                                                                     seqs.data_ptr(), B, B, ptab.data_ptr(), pages, PAGE, cache.data_ptr(), out.data_ptr(), B, splits,
+                                                                                     ws2.data_ptr(), 30, tc, S()))
+            ms = timed(lambda: fn(None, ctx, 0), flush)
+            name = "window_softmax_attn_mma_kernel (+merge)" if tc else "window_softmax_attn_kernel (+merge), CUDA cores"
+            row(name + ", chunk mask, head temperature", f"decode B={B} last position of a chunk of {ctx} heads={H}/{G} splits={splits}",
+                timed(lambda: fn(temp.data_ptr(), 0, ctx), flush), nbytes=nb, peer=peer_of(name + ", window mask", ms, nb))
+    T, ctx = 2048, 4096
+    pages = ctx // PAGE
+    cache = rn(pages + 1, PAGE, cw)
+    ptab = torch.arange(pages, dtype=torch.int32, device=dev).reshape(1, pages)
+    q, out = rn(T, H, d), torch.empty(T, H * dv, dtype=bf, device=dev)
+    pos = torch.arange(ctx - T, ctx, dtype=torch.int32, device=dev)
+    slot = torch.zeros(T, dtype=torch.int32, device=dev)
+    seqs = torch.tensor([[0], [T], [-1], [-1]], dtype=torch.int32, device=dev)
+    fn = lambda hs, win, ch: native.check_seq(seq.ktb200_window_softmax_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, hs, 30.0, win, ch, pos.data_ptr(), slot.data_ptr(), seqs.data_ptr(), 1, 1,
+                                                                             ptab.data_ptr(), pages, PAGE, cache.data_ptr(), out.data_ptr(), T, 1, None, 30, 1, S()))
+    fl = float(sum(range(ctx - T + 1, ctx + 1))) * H * (d + dv) * 2
+    ms = timed(lambda: fn(None, ctx, 0), flush, iters=5, warmup=2)
+    row("window_softmax_attn_mma_kernel, chunk mask, head temperature", f"prompt portion T={T} positions {ctx - T}..{ctx - 1} heads={H}/{G}, one chunk of {ctx}",
+        timed(lambda: fn(temp.data_ptr(), 0, ctx), flush, iters=5, warmup=2), flops=fl, peer=peer_of("window_softmax_attn_mma_kernel, window mask", ms, flops=fl))
+    fl = 2 * float(sum(range(1, 1025))) * H * (d + dv) * 2
+    ms = timed(lambda: fn(None, 1024, 0), flush, iters=5, warmup=2)
+    row("window_softmax_attn_mma_kernel, chunk mask, head temperature", f"the same, chunks of 1024 (half the keys of a window of 1024)",
+        timed(lambda: fn(temp.data_ptr(), 0, 1024), flush, iters=5, warmup=2), flops=fl, peer=peer_of("window_softmax_attn_mma_kernel, window of 1024", ms, flops=float(T) * 1024 * H * (d + dv) * 2))
+
+    # ---- router: 256 experts in 8 groups of which 4 are kept, 8 choices (DeepSeek-V3's shape)  vs  soft-max over all, 8 largest
+    from ..operators.gate import KGroupedSigmoidGate, KSoftmaxTopKGate
+    E, top = 256, 8
+    mine, theirs = KGroupedSigmoidGate(D, E, top, 8, 4, 2.0), KSoftmaxTopKGate(D, E, top)
+    mine.weight.data.copy_(rn(E, D, dt=torch.float32) * D ** -0.5)
+    theirs.weight.data.copy_(mine.weight.data)
+    mine.correction.data.copy_(rn(E, dt=torch.float32) * 0.1)
+    for T in (1, 8, 2048):
+        x = rn(T, D)
+        ours, ms = timed(lambda: mine(x), flush), timed(lambda: theirs(x), flush)
+        nb = E * D * 4 + T * D * 2
+        small = T < mine.gemm_min_tokens
+        row("gate_kernel (sigmoid, correction, groups)" if small else "fp32 GEMM + gate_select_kernel", f"T={T} experts={E} width={D} top={top}", ours, nbytes=nb,
+            peer=peer_of("gate_kernel (soft-max, greedy)" if small else "fp32 GEMM + torch soft-max and top-k", ms, nb))
+
+    # ---- experts: the clamped sigmoid form beside silu(gate) * up in the same kernels
+    E, top, ff = 32, 8, 2048
+    Wg, Wu = rn(E, ff, D) * D ** -0.5, rn(E, ff, D) * D ** -0.5
+    for T in (1, 8):
+        x, act = rn(T, D), torch.empty(T * top, ff, dtype=bf, device=dev)
+        ids = torch.stack([torch.randperm(E, generator=g, device=dev)[:top] for _ in range(T)])
+        uniq = int(ids.unique().numel())
+        fn = lambda kind, lim: native.check_seq(seq.ktb200_experts_gate_up_by_expert(x.data_ptr(), ids.data_ptr(), top, E, Wg.data_ptr(), Wu.data_ptr(), act.data_ptr(), T, D, ff, 0, kind,
+                                                                                     lim, 30, S()))
+        ours, ms = timed(lambda: fn(2, 7.0), flush), timed(lambda: fn(0, 0.0), flush)
+        nb = uniq * 2 * ff * D * 2
+        row("experts_gate_up_by_expert_kernel (clamped sigmoid form)", f"T={T} top={top} width={D} ff={ff} bf16", ours, nbytes=nb,
+            peer=peer_of("experts_gate_up_by_expert_kernel (silu)", ms, nb))
+    # ---- elementwise: expert activation over grouped-GEMM outputs, relu squared, capped logits
+    for P in (64, 2048 * 8):
+        gg, uu, oo = rn(P, ff), rn(P, ff), torch.empty(P, ff, dtype=bf, device=dev)
+        gu = rn(P, 2 * ff)
+        ours = timed(lambda: native.check_seq(seq.ktb200_gated_act_mul(gg.data_ptr(), uu.data_ptr(), ff, oo.data_ptr(), P, ff, 2, 7.0, 30, S())), flush)
+        ms = timed(lambda: native.check_seq(seq.ktb200_gated_act_mul(gu.data_ptr(), gu.data_ptr() + 2 * ff, 2 * ff, oo.data_ptr(), P, ff, 1, 0.0, 30, S())), flush)
+        row("gated_act_mul_kernel (clamped sigmoid form, separate gate and up rows)", f"pairs={P} ff={ff}", ours, nbytes=P * ff * 6,
+            peer=peer_of("gated_act_mul_kernel (gelu_tanh, stacked rows)", ms, P * ff * 6))
+    for T, F_ in ((8, 18432), (2048, 18432)):
+        zz, oo, pq = rn(T, F_), torch.empty(T, F_, dtype=bf, device=dev), torch.tensor([0.3, -0.2], device=dev)
+        ours = timed(lambda: native.check_seq(seq.ktb200_relu_squared(zz.data_ptr(), oo.data_ptr(), zz.numel(), 30, S())), flush)
+        ms = timed(lambda: native.check_seq(seq.ktb200_xielu(zz.data_ptr(), oo.data_ptr(), pq.data_ptr(), zz.numel(), 30, S())), flush)
+        row("relu_squared_kernel", f"T={T} ff={F_}", ours, nbytes=T * F_ * 4, peer=peer_of("xielu_kernel", ms, T * F_ * 4))
+    for T, V in ((8, 32768), (2048, 32768)):
+        zz, of, oo, pq = rn(T, V), torch.empty(T, V, device=dev), torch.empty(T, V, dtype=bf, device=dev), torch.tensor([0.3, -0.2], device=dev)
+        ours = timed(lambda: native.check_seq(seq.ktb200_softcap(zz.data_ptr(), of.data_ptr(), zz.numel(), 30.0, 30, S())), flush)
+        ms = timed(lambda: native.check_seq(seq.ktb200_xielu(zz.data_ptr(), oo.data_ptr(), pq.data_ptr(), zz.numel(), 30, S())), flush)
+        row("softcap_kernel (bf16 in, fp32 out)", f"T={T} vocab={V}", ours, nbytes=T * V * 6, peer=peer_of("xielu_kernel", ms, T * V * 4))
+    return rows
+
+
+def run_bilurax(args):
+    torch.cuda.set_device(0)
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        m = json.load(open(os.path.join(root, "MEASURED_PEAKS.json")))
+        peak, tf, src = float(m["hbm_gbs"]), float(m["bf16_tflops"]), "measured (MEASURED_PEAKS.json hbm_gbs, bf16_tflops)"
+    except Exception:
+        peak, tf, src = 6650.0, 1590.0, "fallback"
+    flush = Flusher("cuda")
+    n0 = native.seq_lib().ktb200_launch_count()
+    out = {"bench": "bilurax", "dtype": "bf16", "data": "synthetic (random weights and tokens)", "hbm_peak_GBps": peak, "bf16_peak_TFLOPs": tf, "peak_source": src,
+           "timing": "CUDA events, median, 256 MB L2 flush between timed calls", "kernels": [] if getattr(args, "no_kernels", False) else bilurax_kernel_leg(flush, peak, tf),
+           "models": [], "closest_models": []}
+    for name in (args.sizes.split(",") if getattr(args, "sizes", None) else BILURAX_SIZES):
+        out["models"].append(engine_leg(name, BILURAX_SIZES[name], flush, args.steps, args.warmup, family="bilurax"))
+        torch.cuda.empty_cache()
+        out["closest_models"].append(engine_leg(name, BILURAX_SIZES[name], flush, args.steps, args.warmup, family="mabidra-attn"))      # Mabidra at the same sizes, in the same process
+        torch.cuda.empty_cache()
+    out["gpu_launches"] = int(native.seq_lib().ktb200_launch_count() - n0)
+    print(json.dumps(out))
+
+
 def run_zivulix(args):
     torch.cuda.set_device(0)
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -615,11 +823,13 @@ def run_zivulix(args):
 
 
 def run(args):
-    """`bench.py --model lekapel | mabidra | zivulix`: prints one JSON line."""
+    """`bench.py --model lekapel | mabidra | zivulix | bilurax`: prints one JSON line."""
     if args.model == "mabidra":
         return run_mabidra(args)
     if args.model == "zivulix":
         return run_zivulix(args)
+    if args.model == "bilurax":
+        return run_bilurax(args)
     torch.cuda.set_device(0)
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     try:

@@ -34,8 +34,8 @@ def token_shift(h, prev, mu):
 
 def chunk_softmax_attention(q, k, v, qpos, kpos, scale, temp, softcap, chunk):
     """q [T, H, d], k [N, G, d], v [N, G, dv].  Query at position i sees the key at position j when j <= i and both lie in the
-    same chunk, floor(i / C) == floor(j / C).  score = scale * temp_h * q.k, squashed to c tanh(score / c); soft-max over the
-    seen keys.  One query, head and key at a time."""
+    same chunk, floor(i / C) == floor(j / C).  score = scale * temp_h * q.k, squashed to c tanh(score / c) when a cap c is given;
+    soft-max over the seen keys.  One query, head and key at a time."""
     T, H, _ = q.shape
     G, dv = k.shape[1], v.shape[2]
     out = torch.zeros(T, H, dv, dtype=q.dtype)
@@ -45,7 +45,8 @@ def chunk_softmax_attention(q, k, v, qpos, kpos, scale, temp, softcap, chunk):
         for h in range(H):
             g = h // (H // G)
             s = torch.stack([(q[t, h] * k[n, g]).sum() for n in seen]) * scale * temp[h]
-            s = softcap * torch.tanh(s / softcap)
+            if softcap is not None:
+                s = softcap * torch.tanh(s / softcap)
             p = torch.exp(s - s.max())
             p = p / p.sum()
             out[t, h] = sum(p[a] * v[n, g] for a, n in enumerate(seen))
@@ -62,7 +63,7 @@ def attention_mixer(h, pos, cache, W, m, eps):
     k = rms_norm(h @ W["k"].T + W["k.b"], W["k.norm"], eps).reshape(T, G, d)
     v = rms((h @ W["v"].T + W["v.b"]).reshape(T, G, dv), eps)
     K, V, P = torch.cat([cache[0], k]), torch.cat([cache[1], v]), torch.cat([cache[2], pos])
-    o = chunk_softmax_attention(q, K, V, pos, P, m["scale"], W["temp"], m["softcap"], m["mask"]["size"])
+    o = chunk_softmax_attention(q, K, V, pos, P, m["scale"], W["temp"], m.get("softcap"), m["mask"]["size"])
     return o.reshape(T, H * dv) @ W["o"].T + W["o.b"], (K, V, P)
 
 
@@ -161,5 +162,5 @@ class Model:
                 trace.append(x.clone())
         state["pos"] += len(tokens)
         z = rms_norm(x, W["final.norm"], eps) @ W["embed"].T
-        cap = c["logit_softcap"]
-        return cap * torch.tanh(z / cap)
+        cap = c.get("logit_softcap")
+        return z if cap is None else cap * torch.tanh(z / cap)
