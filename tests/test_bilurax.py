@@ -532,7 +532,7 @@ def test_drawn_configurations(tmp_path, seed):
     layers = []
     for _ in range(r.randint(1, 5)):
         G = r.choice([1, 2, 4])
-        m = U.attn(heads=G * r.choice([1, 2, 5, 9]), kv_heads=G, dim=r.choice([4, 6, 24, 64]), vdim=r.choice([5, 8, 96]), scale=r.choice([None, 0.11, 1.0]), softcap=r.choice([None, 0.5, 30.0]),
+        m = U.attn(heads=G * r.choice([1, 2, 5, 9]), kv_heads=G, dim=r.choice([4, 6, 24, 64]), vdim=r.choice([5, 8, 80]), scale=r.choice([None, 0.11, 1.0]), softcap=r.choice([None, 0.5, 20.0]),
                    chunk=r.choice([1, 5, 31, 32, 33, 64, 100, 1000]))
         kind = r.random()
         if kind < 0.3:
@@ -543,7 +543,7 @@ def test_drawn_configurations(tmp_path, seed):
             groups = r.choice([1, 2, 4])
             per = r.choice([2, 3, 8])
             keep = r.randint(1, groups)
-            f = U.moe(ff=r.choice([8, 24, 100]), experts=groups * per, top=r.randint(1, min(keep * per, 6)), groups=groups, keep=keep, scale=r.choice([1.0, 2.5]), limit=r.choice([0.5, 1.0, 7.0]))
+            f = U.moe(ff=r.choice([8, 24, 100]), experts=groups * per, top=r.randint(1, min(keep * per, 6)), groups=groups, keep=keep, scale=r.choice([1.0, 2.0]), limit=r.choice([0.5, 1.5, 7.0]))
         layers.append((m, f))
     loop = None
     if r.random() < 0.7:
