@@ -23,42 +23,58 @@
 namespace ktb {
 
 // ------------------------------------------------------------------------------------------------ rotation, unit rms, value blend, cache write
-// One CTA per token, a warp per head (query heads first, then key heads).  The token's rot_dims / 2 angles are turned into
-// (cos, sin) once per CTA (fp64 angle and sincos, kept as fp32) and shared by all heads.
+// grid (tokens, unit blocks): a token's units are its H query heads, then its G key heads, then its G value heads; a CTA takes
+// `units_per_cta` consecutive units, a warp per unit.  Prompt-sized batches run one CTA per token; small batches spread a token's units
+// over several CTAs so that a decode step is not one warp's chain of heads.  What a CTA with query or key units needs of the whole
+// token it computes itself: the rot_dims / 2 (cos, sin) pairs (fp64 angle and sincos, kept as fp32) and, for the row-wide norm, the
+// sums of squares of the whole q row and the whole k row (16- / 8-byte loads where the rows allow them, one fixed order of addition).
 constexpr int kPrepMaxPerLane = 8;      // head size <= 256
 constexpr int kQkNormNone = 0, kQkNormHead = 1, kQkNormRow = 2;
+template <typename T>
+__device__ __forceinline__ float sum_squares(const T* __restrict__ x, int n, bool vec) {
+    float s = 0.f;
+    if (vec) {
+        for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+            const float4 v = load4(x + i);
+            s += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_f(x[i]); s += v * v; }
+    }
+    return s;
+}
 template <typename T>
 __global__ void __launch_bounds__(256) rope_norm_cache_write_kernel(const T* __restrict__ proj, long proj_stride, int q_off, int k_off, int v_off, int H, int G, int d, int dv,
                                                                     int rot_dims, int rot_layout, const double* __restrict__ inv_freq, int qk_norm, const T* __restrict__ q_w,
                                                                     const T* __restrict__ k_w, int v_unit_rms, float eps, const T* __restrict__ v_other, long v_other_stride, const float* __restrict__ blend,
                                                                     const int* __restrict__ pos, const int* __restrict__ slot, const int* __restrict__ page_table,
-                                                                    int max_pages, int page_size, T* __restrict__ cache, T* __restrict__ q_out) {
+                                                                    int max_pages, int page_size, T* __restrict__ cache, T* __restrict__ q_out, int units_per_cta, int vec_rows) {
     __shared__ float2 turn[16 * kPrepMaxPerLane];      // (cos, sin) of the token's angles
     __shared__ float red[8], row_inv[2];
     const long t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int units = H + 2 * G, u0 = blockIdx.y * units_per_cta, u1 = min(units, u0 + units_per_cta);
     const int p = pos[t], half = rot_dims >> 1;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        double sn, cs;
-        sincos((double)p * inv_freq[i], &sn, &cs);
-        turn[i] = make_float2((float)cs, (float)sn);
-    }
-    __syncthreads();
     const T* row = proj + t * proj_stride;
-    if (qk_norm == kQkNormRow) {      // a turn keeps x^2 + y^2 of its pair: the row's mean square is that of the un-turned columns
-        float sq = 0.f, sk = 0.f;
-        for (int i = threadIdx.x; i < H * d; i += blockDim.x) { const float v = to_f(row[q_off + i]); sq += v * v; }
-        for (int i = threadIdx.x; i < G * d; i += blockDim.x) { const float v = to_f(row[k_off + i]); sk += v * v; }
-        sq = block_sum(sq, red);
-        sk = block_sum(sk, red);
-        if (threadIdx.x == 0) {
-            row_inv[0] = 1.0f / sqrtf(sq / (float)(H * d) + eps);
-            row_inv[1] = 1.0f / sqrtf(sk / (float)(G * d) + eps);
+    if (u0 < H + G) {      // this CTA has query or key heads
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            double sn, cs;
+            sincos((double)p * inv_freq[i], &sn, &cs);
+            turn[i] = make_float2((float)cs, (float)sn);
+        }
+        if (qk_norm == kQkNormRow) {      // a turn keeps x^2 + y^2 of its pair: the row's mean square is that of the un-turned columns
+            const float sq = block_sum(sum_squares(row + q_off, H * d, vec_rows), red);
+            const float sk = block_sum(sum_squares(row + k_off, G * d, vec_rows), red);
+            if (threadIdx.x == 0) {
+                row_inv[0] = 1.0f / sqrtf(sq / (float)(H * d) + eps);
+                row_inv[1] = 1.0f / sqrtf(sk / (float)(G * d) + eps);
+            }
         }
         __syncthreads();
     }
     const long crow = ((long)page_table[(long)slot[t] * max_pages + (p / page_size) % max_pages] * page_size + p % page_size) * ((long)G * (d + dv));
-    for (int hh = warp; hh < H + G; hh += nw) {
+    const float lam = v_other ? blend[0] : 0.f;
+    for (int hh = u0 + warp; hh < min(u1, H + G); hh += nw) {
         const bool is_q = hh < H;
         const T* src = is_q ? row + q_off + (long)hh * d : row + k_off + (long)(hh - H) * d;
         float r[kPrepMaxPerLane];
@@ -94,29 +110,27 @@ __global__ void __launch_bounds__(256) rope_norm_cache_write_kernel(const T* __r
             if (i < d) dst[i] = from_f<T>(wrow ? r[e] * inv * to_f(wrow[i]) : r[e] * inv);
         }
     }
-    const T* v = row + v_off;
-    const float lam = v_other ? blend[0] : 0.f;
-    if (v_unit_rms) {      // a warp per value head: mean square over the head's columns, then the scaled columns
-        for (int g = warp; g < G; g += nw) {
+    // value heads: blend, mean square over the head's columns (optional), the scaled columns into the cache
+    for (int hh = max(u0, H + G) + warp; hh < u1; hh += nw) {
+        const int g = hh - H - G;
+        const T* v = row + v_off + (long)g * dv;
+        const T* vo = v_other ? v_other + t * v_other_stride + (long)g * dv : nullptr;
+        T* dst = cache + crow + (long)G * d + (long)g * dv;
+        float inv = 1.f;
+        if (v_unit_rms) {
             float s = 0.f;
             for (int i = lane; i < dv; i += 32) {
-                float x = to_f(v[g * dv + i]);
-                if (v_other) x = (1.0f - lam) * x + lam * to_f(v_other[t * v_other_stride + g * dv + i]);
+                float x = to_f(v[i]);
+                if (vo) x = (1.0f - lam) * x + lam * to_f(vo[i]);
                 s += x * x;
             }
-            const float inv = 1.0f / sqrtf(warp_sum(s) / (float)dv + eps);
-            for (int i = lane; i < dv; i += 32) {
-                float x = to_f(v[g * dv + i]);
-                if (v_other) x = (1.0f - lam) * x + lam * to_f(v_other[t * v_other_stride + g * dv + i]);
-                cache[crow + (long)G * d + g * dv + i] = from_f<T>(x * inv);
-            }
+            inv = 1.0f / sqrtf(warp_sum(s) / (float)dv + eps);
         }
-        return;
-    }
-    for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
-        float x = to_f(v[i]);
-        if (v_other) x = (1.0f - lam) * x + lam * to_f(v_other[t * v_other_stride + i]);
-        cache[crow + (long)G * d + i] = from_f<T>(x);
+        for (int i = lane; i < dv; i += 32) {
+            float x = to_f(v[i]);
+            if (vo) x = (1.0f - lam) * x + lam * to_f(vo[i]);
+            dst[i] = from_f<T>(v_unit_rms ? x * inv : x);
+        }
     }
 }
 
@@ -503,9 +517,17 @@ extern "C" int ktb200_rope_norm_cache_write(const void* proj, long proj_stride, 
         return KTB200_EINVAL;
     }
     if (n_tokens <= 0) return KTB200_OK;
-    SEQ_DISPATCH(dtype, (rope_norm_cache_write_kernel<T><<<n_tokens, 256, 0, (cudaStream_t)stream>>>(
+    // unit blocks per token: as many as keep about a wave of CTAs (148 SMs x 8) busy, eight units (one per warp) at least
+    const int units = heads + 2 * kv_heads, max_y = (units + 7) / 8;
+    int want_y = 1184 / n_tokens;
+    want_y = want_y < 1 ? 1 : (want_y > max_y ? max_y : want_y);
+    const int upc = ((units + want_y - 1) / want_y + 7) / 8 * 8, grid_y = (units + upc - 1) / upc;
+    const size_t esz = dtype == KTB200_TYPE_BF16 ? 2 : 4;
+    const int vec_rows = q_off % 4 == 0 && k_off % 4 == 0 && (heads * dim) % 4 == 0 && (kv_heads * dim) % 4 == 0 && proj_stride % 4 == 0 &&
+                         (reinterpret_cast<uintptr_t>(proj) & (4 * esz - 1)) == 0;
+    SEQ_DISPATCH(dtype, (rope_norm_cache_write_kernel<T><<<dim3(n_tokens, grid_y), 256, 0, (cudaStream_t)stream>>>(
                             (const T*)proj, proj_stride, q_off, k_off, v_off, heads, kv_heads, dim, vdim, rot_dims, rot_layout, inv_freq, qk_norm, (const T*)q_weight, (const T*)k_weight, v_unit_rms, eps,
-                            (const T*)v_other, v_other_stride, blend, pos, slot, page_table, max_pages, page_size, (T*)cache, (T*)q_out)));
+                            (const T*)v_other, v_other_stride, blend, pos, slot, page_table, max_pages, page_size, (T*)cache, (T*)q_out, upc, vec_rows)));
     KTB_LAUNCH_CHECK();
     return KTB200_OK;
 }

@@ -243,7 +243,7 @@ def kernel_leg(flush, peak_gbs, have_main_lib):
         xo, h, hs = torch.empty_like(x), torch.empty(T, D, dtype=bf, device=dev), torch.empty(T, D, dtype=bf, device=dev)
         meta = torch.tensor([[-1] + list(range(T - 1)), [-1] * T, [-1] * (T - 1) + [0]], dtype=torch.int32, device=dev)
         st = torch.zeros(2, D, device=dev)
-        fn = lambda: native.check_seq(seq.ktb200_group_rmsnorm_shift(x.data_ptr(), a.data_ptr(), 30, b.data_ptr(), 30, 0.6, xo.data_ptr(), w.data_ptr(), 4, 1e-5, mu.data_ptr(),
+        fn = lambda: native.check_seq(seq.ktb200_group_rmsnorm_shift(x.data_ptr(), a.data_ptr(), 30, b.data_ptr(), 30, 0.6, None, xo.data_ptr(), w.data_ptr(), 4, 1e-5, mu.data_ptr(),
                                                                      meta[0].data_ptr(), meta[1].data_ptr(), meta[2].data_ptr(), st.data_ptr(), h.data_ptr(), hs.data_ptr(), T, D, 30, S()))
         ours = timed(fn, flush)
         peer = None
@@ -365,7 +365,7 @@ def mabidra_kernel_leg(flush, peak_gbs, peak_tflops):
         a, b, mu, hs = rn(T, D), rn(T, D), rn(D), torch.empty(T, D, dtype=bf, device=dev)
         meta = torch.tensor([[-1] + list(range(T - 1)), [-1] * T, [-1] * (T - 1) + [0]], dtype=torch.int32, device=dev)
         st = torch.zeros(2, D, device=dev)
-        ms = timed(lambda: native.check_seq(seq.ktb200_group_rmsnorm_shift(x.data_ptr(), a.data_ptr(), 30, b.data_ptr(), 30, 0.6, xo.data_ptr(), w1.data_ptr(), 4, 1e-5, mu.data_ptr(),
+        ms = timed(lambda: native.check_seq(seq.ktb200_group_rmsnorm_shift(x.data_ptr(), a.data_ptr(), 30, b.data_ptr(), 30, 0.6, None, xo.data_ptr(), w1.data_ptr(), 4, 1e-5, mu.data_ptr(),
                                                                            meta[0].data_ptr(), meta[1].data_ptr(), meta[2].data_ptr(), st.data_ptr(), h.data_ptr(), hs.data_ptr(), T, D, 30,
                                                                            S())), flush)
         pb = T * D * (4 + 2 + 2 + 4 + 2 + 2)
@@ -524,7 +524,7 @@ def zivulix_kernel_leg(flush, peak_gbs, peak_tflops):
         proj, vo, cache, qo = rn(T, n_in), rn(T, G * dv), rn(pages + 1, PAGE, cw), torch.empty(T, H, d, dtype=bf, device=dev)
         ptab = torch.arange(pages, dtype=torch.int32, device=dev).reshape(1, pages)
         pos, slot = torch.arange(T, dtype=torch.int32, device=dev), torch.zeros(T, dtype=torch.int32, device=dev)
-        ours = timed(lambda: native.check_seq(seq.ktb200_rope_norm_cache_write(proj.data_ptr(), n_in, 0, H * d, (H + G) * d, H, G, d, dv, d // 2, 1, inv.data_ptr(), 1, 1e-6,
+        ours = timed(lambda: native.check_seq(seq.ktb200_rope_norm_cache_write(proj.data_ptr(), n_in, 0, H * d, (H + G) * d, H, G, d, dv, d // 2, 1, inv.data_ptr(), 1, None, None, 0, 1e-6,
                                                                                vo.data_ptr(), G * dv, lam.data_ptr(), pos.data_ptr(), slot.data_ptr(), ptab.data_ptr(), pages, PAGE,
                                                                                cache.data_ptr(), qo.data_ptr(), T, 30, S())), flush)
         qw, kw = rn(d), rn(d)
@@ -557,7 +557,7 @@ def zivulix_kernel_leg(flush, peak_gbs, peak_tflops):
         for tc in (1, 0):
             splits = KCappedWindowAttention.pick_splits(mine, B, ctx, B, bool(tc))
             ws2 = torch.empty(max(1, seq.ktb200_window_softmax_attn_workspace(B, H, dv, splits) // 4), device=dev)
-            fn = lambda: native.check_seq(seq.ktb200_window_softmax_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, 30.0, ctx, pos.data_ptr(), slot.data_ptr(), seqs.data_ptr(), B, B,
+            fn = lambda: native.check_seq(seq.ktb200_window_softmax_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, None, 30.0, ctx, 0, pos.data_ptr(), slot.data_ptr(), seqs.data_ptr(), B, B,
                                                                          ptab.data_ptr(), pages, PAGE, cache.data_ptr(), out.data_ptr(), B, splits, ws2.data_ptr(), 30, tc, S()))
             row("window_softmax_attn_mma_kernel (+merge)" if tc else "window_softmax_attn_kernel (+merge), CUDA cores", f"decode B={B} ctx={ctx} heads={H}/{G} splits={splits}",
                 timed(fn, flush), nbytes=nb, peer=peer)
@@ -575,7 +575,7 @@ def zivulix_kernel_leg(flush, peak_gbs, peak_tflops):
                                                                      seqs.data_ptr(), 1, 1, ptab.data_ptr(), pages, PAGE, cache.data_ptr(), gate.data_ptr(), H, out.data_ptr(), T, 1, None, 30,
                                                                      1, S())), flush, iters=5, warmup=2)
     peer = peer_of("sigmoid_attn_mma_kernel", ms, flops=fl)
-    fn = lambda tc, win: native.check_seq(seq.ktb200_window_softmax_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, 30.0, win, pos.data_ptr(), slot.data_ptr(), seqs.data_ptr(), 1, 1,
+    fn = lambda tc, win: native.check_seq(seq.ktb200_window_softmax_attn(q.data_ptr(), H, G, d, dv, d ** -0.5, None, 30.0, win, 0, pos.data_ptr(), slot.data_ptr(), seqs.data_ptr(), 1, 1,
                                                                          ptab.data_ptr(), pages, PAGE, cache.data_ptr(), out.data_ptr(), T, 1, None, 30, tc, S()))
     row("window_softmax_attn_mma_kernel", f"prompt portion T={T} positions {ctx - T}..{ctx - 1} heads={H}/{G}, every earlier key in sight", timed(lambda: fn(1, ctx), flush, iters=5, warmup=2),
         flops=fl, peer=peer)
